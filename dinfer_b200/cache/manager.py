@@ -30,9 +30,11 @@ from .block_pool import BlockPool, PoolError, StateSlots
 @dataclass(frozen=True)
 class GroupSpec:
     """``window`` None: every token's keys are kept; else the last ``window`` (the token itself counts).
-    ``block_size`` None: the manager's page size; else this group's own."""
+    ``block_size`` None: the manager's page size; else this group's own.  ``keep_first``: with a window, the first
+    so many tokens of a request stay visible behind it, so the pages that hold them are never given back early."""
     window: Optional[int] = None
     block_size: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass
@@ -213,7 +215,8 @@ class CacheManager:
                 continue
             table = held.tables[g]
             stop = min(self._first_needed_block(g, num_computed), len(table))
-            gone = [i for i in range(stop) if table[i] >= 0]
+            kept = (self.groups[g].keep_first + self.block_sizes[g] - 1) // self.block_sizes[g]
+            gone = [i for i in range(kept, stop) if table[i] >= 0]
             self.pools[g].free([table[i] for i in gone])
             for i in gone:
                 table[i] = -1

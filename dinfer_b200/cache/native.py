@@ -29,6 +29,7 @@ def library() -> ctypes.CDLL:
         sig = {
             "dh_last_error": (ctypes.c_char_p, []),
             "dh_manager_new": (P, [I, P, P, P, I, I]), "dh_manager_delete": (None, [P]),
+            "dh_set_keep_first": (I, [P, I, I]),
             "dh_contains": (I, [P, L]), "dh_num_requests": (I, [P]), "dh_requests": (I, [P, P, I]),
             "dh_num_tokens": (I, [P, L]), "dh_num_computed": (I, [P, L]), "dh_table_len": (I, [P, L, I]),
             "dh_table": (I, [P, L, I, P, I]), "dh_pool_free": (I, [P, I]), "dh_pool_blocks": (I, [P, I]),
@@ -129,6 +130,9 @@ class NativeCacheManager:
                                            int(self.prefix_caching))
         if not self._h:
             raise ValueError(_error(self._lib))
+        for g, spec in enumerate(self.groups):
+            if getattr(spec, "keep_first", 0) and self._lib.dh_set_keep_first(self._h, g, int(spec.keep_first)):
+                raise ValueError(_error(self._lib))
         self._ids: Dict[Hashable, int] = {}          # request id -> handle, for the requests that hold something
         self._names: Dict[int, Hashable] = {}
         self._next = 1

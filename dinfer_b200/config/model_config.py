@@ -526,3 +526,192 @@ class ZasipelConfig:
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids)
         return d
+
+
+# ---------------------------------------------------------------- Sobivik
+
+@dataclass(frozen=True)
+class RetentionSizes:
+    """A retention mixer: ``heads`` heads of ``dim`` query/key and ``vdim`` value channels, one fixed ``decay`` a head."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "RetentionSizes":
+        decay = m.get("decay")
+        if not isinstance(decay, (list, tuple)) or not all(isinstance(d, (int, float)) and not isinstance(d, bool) for d in decay):
+            raise ConfigError(f"config.json: {where}'decay' must be a list of numbers")
+        s = cls(heads=_take(m, "heads", int), dim=_take(m, "dim", int), vdim=_take(m, "vdim", int),
+                decay=tuple(float(d) for d in decay))
+        for f in ("heads", "dim", "vdim"):
+            if getattr(s, f) <= 0:
+                raise ConfigError(f"config.json: {where}'{f}' must be positive, got {getattr(s, f)}")
+        if len(s.decay) != s.heads or not all(0.0 <= d <= 1.0 for d in s.decay):
+            raise ConfigError(f"config.json: {where}'decay' must hold one number between 0 and 1 for each of the {s.heads} heads")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "vdim": self.vdim, "decay": list(self.decay)}
+
+
+@dataclass(frozen=True)
+class RampScaling:
+    """A rotation stretched to ``factor`` times the ``original`` length by a ramp over its frequencies: those that make
+    more than ``fast`` turns over the original length stay, those that make fewer than ``slow`` are divided by the
+    factor."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "RampScaling":
+        s = cls(*(_take(m, k, float) for k in ("factor", "original", "fast", "slow")))
+        if not (s.factor > 0 and s.original > 0 and s.fast > 0 and s.slow > 0):
+            raise ConfigError(f"config.json: {where}rot.scaling: factor, original, fast and slow must be positive")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"factor": self.factor, "original": self.original, "fast": self.fast, "slow": self.slow}
+
+
+@dataclass(frozen=True)
+class WindowLatentSizes:
+    """Latent attention (``LatentAttentionSizes``) over a sliding window, with a learned sink per head, an output gate
+    and a rotation in halves (element i with i + dims / 2), optionally stretched (``scaling``)."""
+    latent: LatentAttentionSizes
+    window: int
+    scaling: Optional[RampScaling]
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "WindowLatentSizes":
+        latent = LatentAttentionSizes.from_dict(m, where)
+        if latent.kv_from is not None:
+            raise ConfigError(f"config.json: {where}kv_from is not part of this design")
+        sc = _section(_section(m, "rot", where), "scaling", where, optional=True)
+        s = cls(latent, _take(_section(m, "mask", where), "size", int), RampScaling.from_dict(sc, where) if sc else None)
+        if s.window <= 0:
+            raise ConfigError(f"config.json: {where}mask.size must be positive, got {s.window}")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        m = self.latent
+        rot = {"base": m.rot_base, "dims": m.rot_dims}
+        if self.scaling:
+            rot["scaling"] = self.scaling.to_dict()
+        return {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim, "kv_rank": m.kv_rank,
+                "q_rank": m.q_rank, "scale": m.scale, "rot": rot, "mask": {"size": self.window}}
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSizes:
+    """Differential attention: ``heads`` query heads and ``kv_heads`` key/value heads, two score maps of ``dim``
+    elements each per head, values of ``vdim``; a window of ``window`` tokens behind which the first ``keep_first``
+    tokens stay visible; ``diff``: the constant of lambda and of the output factor."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int
+    keep_first: int
+    diff: float
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "DifferentialAttentionSizes":
+        mask = _section(m, "mask", where)
+        s = cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                vdim=_take(m, "vdim", int), scale=_take(m, "scale", float), window=_take(mask, "size", int),
+                keep_first=_take(mask, "keep_first", int, 0), diff=_take(m, "diff", float))
+        for f in ("heads", "kv_heads", "dim", "vdim", "window"):
+            if getattr(s, f) <= 0:
+                raise ConfigError(f"config.json: {where}'{f}' must be positive, got {getattr(s, f)}")
+        if s.heads % s.kv_heads:
+            raise ConfigError(f"config.json: {where}heads {s.heads} must be a multiple of kv_heads {s.kv_heads}")
+        if s.keep_first < 0:
+            raise ConfigError(f"config.json: {where}mask.keep_first must not be negative")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
+                "diff": self.diff, "mask": {"size": self.window, "keep_first": self.keep_first}}
+
+
+@dataclass(frozen=True)
+class SobivikLayer:
+    """``type``: "retention", "latent_attention" or "attention" (differential); ``mixer``: that mixer's sizes;
+    ``mlp``: a dense gated feed-forward or none."""
+    type: str
+    mixer: Any
+    mlp: Optional[FeedForwardSizes]
+
+
+@dataclass(frozen=True)
+class SobivikConfig:
+    """``config.json`` of a Sobivik model: ``vocab``, ``width``, ``norm.eps``, ``embedding.scale``, ``logit_scale``,
+    ``canon.taps`` (the short convolution on every mixer's input) and the list ``layers``, each entry with its
+    ``type`` (the mixer it has), the mixer's sizes and its feed-forward (``mlp``, or null).  ``max_positions`` is
+    optional: the design has no longest sequence of its own."""
+    vocab: int
+    width: int
+    norm_eps: float
+    embedding_scale: float
+    logit_scale: float
+    conv_taps: int
+    layers: Tuple[SobivikLayer, ...]
+    max_positions: int = 1 << 20
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Sobivik"
+
+    MIXER_TYPES = {"retention": RetentionSizes, "latent_attention": WindowLatentSizes, "attention": DifferentialAttentionSizes}
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "SobivikConfig":
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, l in enumerate(raw):
+            where = f"layers[{i}]: "
+            if not isinstance(l, dict):
+                raise ConfigError(f"config.json: {where}must be an object")
+            kind = _take(l, "type", str)
+            if kind not in cls.MIXER_TYPES:
+                raise ConfigError(f"config.json: {where}unknown type {kind!r} ({', '.join(cls.MIXER_TYPES)})")
+            mixer = cls.MIXER_TYPES[kind].from_dict(_section(l, "mixer", where), where)
+            mlp = _section(l, "mlp", where, optional=True)
+            ff = FeedForwardSizes.from_dict(mlp, where) if mlp else None
+            if ff is not None and ff.kind != "dense":
+                raise ConfigError(f"config.json: {where}mlp.kind {ff.kind!r}: the design's feed-forward is dense")
+            layers.append(SobivikLayer(kind, mixer, ff))
+        eos = d.get("eos_token_id")
+        eos_ids = (eos,) if isinstance(eos, int) and not isinstance(eos, bool) else \
+            tuple(int(x) for x in eos) if isinstance(eos, (list, tuple)) else ()
+        cfg = cls(vocab=_take(d, "vocab", int), width=_take(d, "width", int),
+                  norm_eps=_take(_section(d, "norm", ""), "eps", float),
+                  embedding_scale=_take(_section(d, "embedding", ""), "scale", float),
+                  logit_scale=_take(d, "logit_scale", float),
+                  conv_taps=_take(_section(d, "canon", ""), "taps", int), layers=tuple(layers),
+                  max_positions=_take(d, "max_positions", int, 1 << 20), eos_token_ids=eos_ids,
+                  architecture=str(d.get("architecture") or (d.get("architectures") or ["Sobivik"])[0]))
+        if cfg.vocab <= 0 or cfg.width <= 0 or cfg.max_positions <= 1:
+            raise ConfigError("config.json: vocab, width and max_positions must be positive")
+        if not cfg.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {cfg.norm_eps}")
+        if not (1 <= cfg.conv_taps <= 16):
+            raise ConfigError(f"config.json: canon.taps must be between 1 and 16, got {cfg.conv_taps}")
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        layers = [{"type": l.type, "mixer": l.mixer.to_dict(),
+                   "mlp": {"kind": "dense", "ff": l.mlp.ff} if l.mlp is not None else None} for l in self.layers]
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+             "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale,
+             "canon": {"taps": self.conv_taps}, "layers": layers}
+        if self.max_positions != 1 << 20:
+            d["max_positions"] = self.max_positions
+        if self.eos_token_ids:
+            d["eos_token_id"] = list(self.eos_token_ids)
+        return d

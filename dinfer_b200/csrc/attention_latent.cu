@@ -26,7 +26,8 @@ attention_latent_generic_kernel(const T* __restrict__ q, int64_t ldq_t, int64_t 
                                 int64_t ldo_t, int64_t ldo_h, const T* __restrict__ cache,
                                 const int* __restrict__ block_table, int max_blocks,
                                 const int* __restrict__ cu_seqlens, const int* __restrict__ positions, int num_reqs,
-                                int H, int R, int P, int block_size, float scale, int window) {
+                                int H, int R, int P, int block_size, float scale, int window,
+                                const float* __restrict__ sinks) {
   pdl_enter();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -92,6 +93,14 @@ attention_latent_generic_kernel(const T* __restrict__ q, int64_t ldq_t, int64_t 
     }
     m = m_new;
   }
+  if (sinks) {                                                    // one more term, exp(sink_h), in the denominator only
+    const float sk = sinks[h];
+    const float m_new = fmaxf(m, sk);
+    const float alpha = m == -INFINITY ? 0.f : expf(m - m_new);
+    l = l * alpha + expf(sk - m_new);
+#pragma unroll
+    for (int c = 0; c < C; ++c) acc[c] *= alpha;
+  }
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int c = 0; c < C; ++c) {
@@ -104,11 +113,11 @@ template <typename T, int C>
 int launch_generic(const void* q, int64_t ldq_t, int64_t ldq_h, void* out, int64_t ldo_t, int64_t ldo_h,
                    const void* cache, const int* block_table, int max_blocks, const int* cu_seqlens,
                    const int* positions, int T_, int B, int H, int R, int P, int block_size, float scale, int window,
-                   cudaStream_t stream) {
+                   const float* sinks, cudaStream_t stream) {
   dim3 grid(T_, (H + WARPS - 1) / WARPS);
   launch_pdl(attention_latent_generic_kernel<T, C>, grid, dim3(WARPS * 32), 0, stream, (const T*)q, ldq_t, ldq_h,
              (T*)out, ldo_t, ldo_h, (const T*)cache, block_table, max_blocks, cu_seqlens, positions, B, H, R, P,
-             block_size, scale, window);
+             block_size, scale, window, sinks);
   return cuda_status("attention_latent_generic");
 }
 
@@ -118,12 +127,12 @@ DINFER_DEFINE_LAST_ERROR()
 
 // q [T, H, R + P] with element strides (ldq_t, ldq_h); out [T, H, R] with (ldo_t, ldo_h); cache
 // [pages, block_size, R + P] contiguous; block_table [B, max_blocks] int32; cu_seqlens [B + 1]; positions [T].
-// window <= 0: all keys.
+// window <= 0: all keys.  sinks [H] f32 or null: the softmax of head h has one more term exp(sinks[h]) that carries no value.
 DINFER_API int dinfer_attention_latent_generic(const void* q, int64_t ldq_t, int64_t ldq_h, void* out, int64_t ldo_t,
                                                int64_t ldo_h, const void* cache, const int* block_table,
                                                int max_blocks, const int* cu_seqlens, const int* positions, int T,
                                                int B, int H, int R, int P, int block_size, float scale, int window,
-                                               int dtype, cudaStream_t stream) {
+                                               const float* sinks, int dtype, cudaStream_t stream) {
   if (T < 0 || B <= 0 || H <= 0 || R <= 0 || P < 0 || block_size <= 0 || max_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_latent_generic: bad sizes T=%d B=%d H=%d R=%d P=%d block=%d", T, B, H,
                   R, P, block_size);
@@ -132,7 +141,7 @@ DINFER_API int dinfer_attention_latent_generic(const void* q, int64_t ldq_t, int
   if (T == 0) return 0;
   const int c = (R + P + 31) / 32;
 #define GO(C) return launch_generic<T_, C>(q, ldq_t, ldq_h, out, ldo_t, ldo_h, cache, block_table, max_blocks, \
-                                           cu_seqlens, positions, T, B, H, R, P, block_size, scale, window, stream)
+                                           cu_seqlens, positions, T, B, H, R, P, block_size, scale, window, sinks, stream)
   DINFER_DISPATCH_DTYPE(dtype, T_, {
     if (c <= 1) GO(1);
     else if (c <= 2) GO(2);
@@ -198,6 +207,7 @@ struct LatentTcParams {
   float scale_log2;
   float* part;                   // [T * H, splits, R] unnormalised sums (splits > 1)
   float* ml;                     // [T * H, splits, 2] maximum (log2 domain) and sum
+  const float* sinks;            // [H] or null: one more term exp(sinks[h]) in head h's denominator, without a value
 };
 
 // NB: buffers of the key tile (2: the next tile is fetched while this one is worked on; 1: where 64 query rows of a wide
@@ -406,8 +416,10 @@ attention_latent_tc_kernel(const LatentTcParams p) {
       if (gr >= rows) continue;
       const int64_t tok = t0 + gr / p.H;
       const int head = gr % p.H;
-      const float l = l_s[row];
+      float l = l_s[row];
       if (p.splits == 1) {
+        // the sink joins where the row is normalised: l holds the sum of 2^(s - m), so its term is 2^(sink log2(e) - m)
+        if (p.sinks && l > 0.f) l += exp2f(p.sinks[head] * LOG2E - m_s[row]);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst = p.out + tok * p.ldo_t + (int64_t)head * p.ldo_h;
 #pragma unroll
@@ -432,7 +444,8 @@ attention_latent_tc_kernel(const LatentTcParams p) {
 // out[row] = sum_s 2^(m_s - M) part[row, s] / sum_s 2^(m_s - M) l_s, in split order; one block per (token, head)
 __global__ void __launch_bounds__(128)
 attention_latent_fold_kernel(const float* __restrict__ part, const float* __restrict__ ml, __nv_bfloat16* __restrict__ out,
-                             int64_t ldo_t, int64_t ldo_h, int rows, int H, int R, int splits) {
+                             int64_t ldo_t, int64_t ldo_h, int rows, int H, int R, int splits,
+                             const float* __restrict__ sinks) {
   __shared__ float w_s[64];
   __shared__ float inv_s;
   pdl_enter();
@@ -448,6 +461,7 @@ attention_latent_fold_kernel(const float* __restrict__ part, const float* __rest
     if (lane == 0) {
       float L = 0.f;
       for (int s = 0; s < splits; ++s) L += w_s[s] * mlr[2 * s + 1];
+      if (sinks && L > 0.f) L += exp2f(sinks[row % H] * LOG2E - M);
       inv_s = L > 0.f ? 1.f / L : 0.f;
     }
   }
@@ -494,7 +508,7 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
                                           int64_t ldo_h, const void* cache, const int* block_table, int max_blocks,
                                           const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int R, int P,
                                           int block_size, float scale, int window, int max_rows_per_req, int row_tiles,
-                                          int splits, float* part, float* ml, cudaStream_t stream) {
+                                          int splits, float* part, float* ml, const float* sinks, cudaStream_t stream) {
   if (T < 0 || B <= 0 || H <= 0 || R <= 0 || P < 0 || block_size <= 0 || max_blocks <= 0 || splits <= 0 || row_tiles < 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: bad sizes T=%d B=%d H=%d R=%d P=%d", T, B, H, R, P);
   if (R % 16 || P % 16 || R > 512 || ldq_t % 8 || ldq_h % 8 || ldo_t % 2 || ldo_h % 2 ||
@@ -509,7 +523,7 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
   p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.max_blocks = max_blocks;
   p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.num_reqs = B; p.H = H; p.R = R; p.P = P;
   p.block_size = block_size; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
-  p.part = part; p.ml = ml;
+  p.part = part; p.ml = ml; p.sinks = sinks;
   const int bm = dinfer_attention_latent_tc_rows(R, max_rows_per_req);
   const int nt = (R + 8 * TC_WARPS - 1) / (8 * TC_WARPS);      // n-tiles of the output a warp owns
   int rc;
@@ -520,6 +534,6 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
 #undef GO
   if (rc != 0 || splits == 1) return rc;
   launch_pdl(attention_latent_fold_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part, (const float*)ml,
-             (__nv_bfloat16*)out, ldo_t, ldo_h, T * H, H, R, splits);
+             (__nv_bfloat16*)out, ldo_t, ldo_h, T * H, H, R, splits, sinks);
   return cuda_status("attention_latent_fold");
 }

@@ -42,6 +42,10 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_latent": ("attention_latent.cu", []),
     "moe": ("moe.cu", []),
     "delta_rule": ("delta_rule.cu", []),
+    "retention": ("retention.cu", []),
+    "short_conv": ("short_conv.cu", []),
+    "attention_diff": ("attention_diff.cu", []),
+    "sandwich": ("sandwich.cu", []),
     # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
     "host_core": ("host_core.cpp", []),
 }

@@ -30,6 +30,22 @@ __global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap) {
     x[i] = cap * tanhf(x[i] * inv);
 }
 
+__global__ void scale_kernel(float* __restrict__ x, int64_t n, float f) {
+  pdl_enter();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] *= f;
+}
+
+// x[t, i] *= sigmoid(gate[t, i / group]) in 32-bit, one rounding
+template <typename T, typename TG>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int64_t ldx, const TG* __restrict__ gate, int64_t ldg, int N, int group) {
+  pdl_enter();
+  const int64_t t = blockIdx.x;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < N; i += gridDim.y * blockDim.x) {
+    const float g = to_f32<TG>(gate[t * ldg + i / group]);
+    x[t * ldx + i] = from_f32<T>(to_f32<T>(x[t * ldx + i]) / (1.f + expf(-g)));
+  }
+}
+
 // out[t, i] = silu(gate_i) * up_i; silu(g) = g / (1 + exp(-g)) in 32-bit, one rounding.  The row of x holds
 // gate and up as two halves (gate_i at i, up_i at I + i) or in pairs (gate_i at 2i, up_i at 2i + 1).
 template <typename T>
@@ -206,6 +222,31 @@ DINFER_API int dinfer_softcap(float* x, int64_t n, float cap, cudaStream_t strea
   if (blocks > 4096) blocks = 4096;
   launch_pdl(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, cap);
   return cuda_status("softcap");
+}
+
+// x[i] *= f in place over n 32-bit values (logits with a fixed factor)
+DINFER_API int dinfer_scale(float* x, int64_t n, float f, cudaStream_t stream) {
+  if (n < 0) return refuse(DINFER_BAD_ARGUMENT, "scale: n=%lld", (long long)n);
+  if (n == 0) return 0;
+  int64_t blocks = (n + 1023) / 1024;
+  if (blocks > 4096) blocks = 4096;
+  launch_pdl(scale_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, f);
+  return cuda_status("scale");
+}
+
+// x [T, N] (row stride ldx) *= sigmoid(gate [T, N / group] (row stride ldg)): one gate per `group` neighbouring elements
+DINFER_API int dinfer_sigmoid_gate(void* x, int64_t ldx, const void* gate, int64_t ldg, int T, int N, int group, int dtype,
+                                   int gate_dtype, cudaStream_t stream) {
+  if (T < 0 || N <= 0 || group <= 0 || N % group || ldx < N || ldg < N / group)
+    return refuse(DINFER_BAD_ARGUMENT, "sigmoid_gate: bad sizes T=%d N=%d group=%d", T, N, group);
+  if (T == 0) return 0;
+  dim3 grid(T, (N + 1023) / 1024 > 64 ? 64 : (N + 1023) / 1024);
+  DINFER_DISPATCH_DTYPE(dtype, TA,
+    DINFER_DISPATCH_DTYPE(gate_dtype, TG, {
+      launch_pdl(sigmoid_gate_kernel<TA, TG>, grid, dim3(256), 0, stream, (TA*)x, ldx, (const TG*)gate, ldg, N, group);
+      return cuda_status("sigmoid_gate");
+    }));
+  return 0;
 }
 
 // out [T, N] (row stride ld, act dtype) += bias [N] (bias dtype)

@@ -144,6 +144,7 @@ struct Held {
 
 struct Manager {
   std::vector<int> windows;                      // per group: 0 = every key is kept
+  std::vector<int> keep_first;                   // per group: with a window, the first so many tokens stay
   std::vector<int> block_sizes;                  // per group: tokens a page holds (one size for all with the prefix cache on)
   std::vector<Pool> pools;
   bool prefix = false;
@@ -237,6 +238,7 @@ DH_API void* dh_manager_new(int n_groups, const int* windows, const int* block_s
   }
   auto* m = new Manager();
   m->windows.assign(windows, windows + n_groups);
+  m->keep_first.assign(n_groups, 0);
   m->block_sizes.assign(block_sizes, block_sizes + n_groups);
   for (int g = 0; g < n_groups; ++g) {
     if (num_blocks[g] <= 0) { delete m; fail("a pool needs at least one block"); return nullptr; }
@@ -368,9 +370,16 @@ DH_API int dh_advance(void* mp, int64_t r, int num_computed, const int32_t* new_
     if (!m->windows[g]) continue;
     auto& t = h->tables[g];
     const int stop = std::min(m->first_needed_block((int)g, num_computed), (int)t.size());
-    for (int i = 0; i < stop; ++i)
+    for (int i = (m->keep_first[g] + m->block_sizes[g] - 1) / m->block_sizes[g]; i < stop; ++i)
       if (t[i] >= 0) { if (m->pools[g].release(t[i])) return -1; t[i] = -1; }
   }
+  return 0;
+}
+// Group g keeps the first n tokens of every request behind its window (set before any request is admitted).
+DH_API int dh_set_keep_first(void* mp, int g, int n) {
+  auto* m = static_cast<Manager*>(mp);
+  if (g < 0 || g >= (int)m->keep_first.size() || n < 0) return fail("group %lld / keep_first %lld out of range", (long long)g, n);
+  m->keep_first[g] = n;
   return 0;
 }
 DH_API int dh_resolve(void* mp, int64_t r, const int32_t* tokens, int n) {

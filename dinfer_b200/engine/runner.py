@@ -184,7 +184,7 @@ class ModelRunner:
             # a model without any paged cache (recurrent mixers only): one group that no layer stores into keeps
             # the bookkeeping of a request's length in pages, which the scheduler budgets by, as it is
             group_keys.append(("kv", None, None))
-        groups = [GroupSpec(window=k[1], block_size=k[2]) for k in group_keys]
+        groups = [GroupSpec(window=k[1], block_size=k[2], keep_first=k[3] if len(k) > 3 else 0) for k in group_keys]
         sizes = [k[2] or bs for k in group_keys]             # tokens a page of each group holds
         if any(b <= 0 for b in sizes):
             raise ValueError("a cache group's block_size must be positive")

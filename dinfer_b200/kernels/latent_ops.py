@@ -12,7 +12,8 @@ from .ops import _fn, _rows_contiguous
 
 def latent_down_post(x: torch.Tensor, positions: torch.Tensor, q_weight: torch.Tensor, q_rank: int,
                      kv_weight: Optional[torch.Tensor], kv_rank: int, rope_dim: int, eps: float,
-                     cos_sin: Optional[torch.Tensor], cache: Optional[torch.Tensor], slots: Optional[torch.Tensor]) -> None:
+                     cos_sin: Optional[torch.Tensor], cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                     halves: bool = False) -> None:
     """Rows ``x`` [T, q_rank (+ kv_rank + rope_dim)] of the stacked down projections: the q latent is RMS-normed in
     place; with a kv part, the normed kv latent and the rotated shared key part (pairs (2i, 2i + 1), angles from the
     ``cos_sin`` table row of the token's position) go into the token's row ``slots[t]`` of the latent ``cache``
@@ -38,14 +39,14 @@ def latent_down_post(x: torch.Tensor, positions: torch.Tensor, q_weight: torch.T
             rot = cos_sin.shape[1]
     lib, f = _fn("latent_post", "dinfer_latent_down_post",
                  [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                  c_int, c_int, c_float, c_int, c_int, c_void_p])
+                  c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
     check(lib, f(ptr(x), x.stride(0), ptr(positions), ptr(q_weight), ptr(kv_weight), ptr(cos_sin) if has_kv else None,
                  rot, ptr(cache) if has_kv else None, ptr(slots) if has_kv else None, T, q_rank, R, P, float(eps),
-                 dtype_code(x.dtype), dtype_code(q_weight.dtype), stream_handle()), "latent_down_post")
+                 int(bool(halves)), dtype_code(x.dtype), dtype_code(q_weight.dtype), stream_handle()), "latent_down_post")
 
 
 def latent_q_rope(q: torch.Tensor, positions: torch.Tensor, cos_sin: Optional[torch.Tensor], q_lat: torch.Tensor,
-                  num_heads: int, nope_dim: int, rope_dim: int, kv_rank: int) -> None:
+                  num_heads: int, nope_dim: int, rope_dim: int, kv_rank: int, halves: bool = False) -> None:
     """The last ``rope_dim`` elements of every head of ``q`` [T, H * (nope_dim + rope_dim)], rotated by the token's
     position, into ``q_lat[t, h, kv_rank:]`` (q_lat [T, H, kv_rank + rope_dim], any token and head strides)."""
     require_cuda(q, positions, cos_sin, q_lat)
@@ -61,10 +62,10 @@ def latent_q_rope(q: torch.Tensor, positions: torch.Tensor, cos_sin: Optional[to
         rot = cos_sin.shape[1]
     lib, f = _fn("latent_post", "dinfer_latent_q_rope",
                  [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
-                  c_int, c_void_p])
+                  c_int, c_int, c_void_p])
     check(lib, f(ptr(q), q.stride(0), ptr(positions), ptr(cos_sin), rot, ptr(q_lat), q_lat.stride(0), q_lat.stride(1), T,
                  num_heads, nope_dim, rope_dim,
-                 kv_rank, dtype_code(q.dtype), stream_handle()), "latent_q_rope")
+                 kv_rank, int(bool(halves)), dtype_code(q.dtype), stream_handle()), "latent_q_rope")
 
 
 def _check_attention(q_lat, out, cache, block_table, cu_seqlens, kv_rank, rope_dim):
@@ -84,21 +85,31 @@ def _check_attention(q_lat, out, cache, block_table, cu_seqlens, kv_rank, rope_d
     return T, H
 
 
+def _check_sinks(sinks, H):
+    if sinks is not None:
+        require_cuda(sinks)
+        if sinks.dtype != torch.float32 or sinks.numel() != H or not sinks.is_contiguous():
+            raise KernelError("attention_latent: sinks float32 [H] contiguous")
+
+
 def attention_latent_generic(q_lat: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                              cu_seqlens: torch.Tensor, positions: torch.Tensor, kv_rank: int, rope_dim: int,
-                             scale: float, window: int = 0) -> torch.Tensor:
+                             scale: float, window: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal multi-query attention in the absorbed form over the paged latent cache, plain arithmetic, any sizes:
-    ``out[t, h] = sum_j softmax_j((q_lat[t, h] . row_j) * scale) row_j[:kv_rank]``."""
+    ``out[t, h] = sum_j softmax_j((q_lat[t, h] . row_j) * scale) row_j[:kv_rank]``.  ``sinks`` f32 [H]: head h's
+    softmax has one more term ``exp(sinks[h])`` that carries no value."""
     T, H = _check_attention(q_lat, out, cache, block_table, cu_seqlens, kv_rank, rope_dim)
     require_cuda(positions)
+    _check_sinks(sinks, H)
     if positions.dtype != torch.int32 or positions.numel() != T:
         raise KernelError("attention_latent: positions int32 [T]")
     lib, f = _fn("attention_latent", "dinfer_attention_latent_generic",
                  [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p])
     check(lib, f(ptr(q_lat), q_lat.stride(0), q_lat.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(cache),
                  ptr(block_table), block_table.shape[1], ptr(cu_seqlens), ptr(positions), T, cu_seqlens.numel() - 1, H,
-                 kv_rank, rope_dim, cache.shape[-2], float(scale), int(window), dtype_code(q_lat.dtype), stream_handle()),
+                 kv_rank, rope_dim, cache.shape[-2], float(scale), int(window), ptr(sinks), dtype_code(q_lat.dtype),
+                 stream_handle()),
           "attention_latent_generic")
     return out
 
@@ -125,13 +136,15 @@ def tc_splits(row_tiles: int, max_seq_len: int) -> int:
 
 def attention_latent_tc(q_lat: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                         cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, kv_rank: int, rope_dim: int, scale: float,
-                        window: int = 0, max_q_len: int = 1, max_seq_len: int = 1, splits: Optional[int] = None) -> torch.Tensor:
+                        window: int = 0, max_q_len: int = 1, max_seq_len: int = 1, splits: Optional[int] = None,
+                        sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same attention on tensor cores (bfloat16): prompt portions and decoded tokens in one launch.  ``seq_lens`` [B]:
     tokens of each request after the step (a token's position follows from it); ``max_q_len``: the longest portion of
     the batch (chooses the row tile); ``max_seq_len``: the longest request (chooses how many CTAs share a row tile's keys
     unless ``splits`` says)."""
     T, H = _check_attention(q_lat, out, cache, block_table, cu_seqlens, kv_rank, rope_dim)
     require_cuda(seq_lens)
+    _check_sinks(sinks, H)
     B = cu_seqlens.numel() - 1
     if seq_lens.dtype != torch.int32 or seq_lens.numel() < B or not seq_lens.is_contiguous():
         raise KernelError("attention_latent_tc: seq_lens int32 [B]")
@@ -148,11 +161,12 @@ def attention_latent_tc(q_lat: torch.Tensor, out: torch.Tensor, cache: torch.Ten
         ml = torch.empty((T * H * splits * 2,), dtype=torch.float32, device=q_lat.device)
     lib, f = _fn("attention_latent", "dinfer_attention_latent_tc",
                  [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                  c_void_p])
     check(lib, f(ptr(q_lat), q_lat.stride(0), q_lat.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(cache),
                  ptr(block_table), block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), T, B, H, kv_rank, rope_dim,
                  cache.shape[-2], float(scale), int(window), rows_per_req, row_tiles, int(splits), ptr(part), ptr(ml),
-                 stream_handle()), "attention_latent_tc")
+                 ptr(sinks), stream_handle()), "attention_latent_tc")
     if splits > 1:
         from .lib import add_launches
         add_launches(1)                                   # the fold kernel

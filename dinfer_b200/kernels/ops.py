@@ -61,6 +61,32 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+def scale(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (float32, contiguous): logits with a fixed factor."""
+    require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale: contiguous float32 values")
+    lib, f = _fn("elementwise", "dinfer_scale", [c_void_p, c_int64, c_float, c_void_p])
+    check(lib, f(ptr(x), x.numel(), float(factor), stream_handle()), "scale")
+    return x
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, group: int = 1) -> torch.Tensor:
+    """``x[t, i] *= sigmoid(gate[t, i // group])`` in place: one gate per element (``group`` 1) or per ``group``
+    neighbouring elements (a head).  Rows of either may have a stride."""
+    require_cuda(x, gate)
+    _rows_contiguous(x, "sigmoid_gate")
+    _rows_contiguous(gate, "sigmoid_gate")
+    T, N = x.shape
+    if gate.shape[0] != T or N % group or gate.shape[1] != N // group:
+        raise KernelError("sigmoid_gate: x [T, N], gate [T, N / group]")
+    lib, f = _fn("elementwise", "dinfer_sigmoid_gate",
+                 [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(x), x.stride(0), ptr(gate), gate.stride(0), T, N, int(group), dtype_code(x.dtype),
+                 dtype_code(gate.dtype), stream_handle()), "sigmoid_gate")
+    return x
+
+
 def rmsnorm(residual: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[r] = rmsnorm(residual[src] + delta[src]) * weight, src = rows[r] or r; the sum is written
@@ -410,4 +436,42 @@ def gemm_f32_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> tor
     check(lib, f(ptr(a), a.stride(0), a.stride(1), dtype_code(a.dtype), ptr(w), w.stride(1), w.stride(0),
                  dtype_code(w.dtype), ptr(out), out.stride(0), out.stride(1), dtype_code(out.dtype), M, N, K, B,
                  stream_handle()), "gemm_f32_batched")
+    return out
+
+
+def attention_diff(q: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], cache: torch.Tensor,
+                   block_table: torch.Tensor, cu_seqlens: torch.Tensor, positions: torch.Tensor, num_heads: int,
+                   num_kv_heads: int, head_dim: int, v_dim: int, scale: float, window: int, keep_first: int,
+                   lam: float, eps: float, out_scale: float) -> torch.Tensor:
+    """Differential attention over the paged cache, plain arithmetic, any sizes: per head two softmax maps (queries and
+    keys ``[map 1 | map 2]``, ``head_dim`` each) over the same values, ``o = a1 - lam * a2``, then ``o / rms(o) *
+    out_scale * sigmoid(gate[t, h])``.  A query at p sees j <= p with p - j < window or j < keep_first.  ``q`` [T, H * 2 D]
+    and ``gate`` [T, H] may be strided views of one projection's rows; cache rows are ``max(2 D, v_dim)`` wide."""
+    require_cuda(q, out, gate, cache, block_table, cu_seqlens, positions)
+    _rows_contiguous(q, "attention_diff q")
+    _rows_contiguous(out, "attention_diff out")
+    T = q.shape[0]
+    B = cu_seqlens.numel() - 1
+    row = max(2 * head_dim, v_dim)
+    if q.dtype != cache.dtype or out.dtype != q.dtype or (gate is not None and (gate.dtype != q.dtype or gate.stride(1) != 1
+                                                                                or tuple(gate.shape) != (T, num_heads))):
+        raise KernelError("attention_diff: q, out, gate [T, H] and cache must have one dtype")
+    if q.shape[1] != num_heads * 2 * head_dim or tuple(out.shape) != (T, num_heads * v_dim):
+        raise KernelError("attention_diff: q [T, H * 2 D], out [T, H * Dv]")
+    for t, n in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"attention_diff: {n} must be contiguous int32")
+    if block_table.dim() != 2 or block_table.shape[0] < B or positions.numel() != T:
+        raise KernelError("attention_diff: block_table [B, max_blocks], positions [T]")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != row \
+            or not cache.is_contiguous():
+        raise KernelError(f"attention_diff: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, {row}]")
+    lib, f = _fn("attention_diff", "dinfer_attention_diff",
+                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_float,
+                  c_int, c_void_p])
+    check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
+                 ptr(cache), ptr(block_table), block_table.shape[1], ptr(cu_seqlens), ptr(positions), T, B, num_heads,
+                 num_kv_heads, head_dim, v_dim, row, cache.shape[3], float(scale), int(window or 0), int(keep_first or 0),
+                 float(lam), float(eps), float(out_scale), dtype_code(q.dtype), stream_handle()), "attention_diff")
     return out

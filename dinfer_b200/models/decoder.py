@@ -11,8 +11,8 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from ..parts import (attention, block, delta_rule, latent_attention, mlp, moe, norm, parallel_mixers,  # noqa: F401
-                     rope)                                # (register the built-in parts)
+from ..parts import (attention, block, delta_rule, differential_attention, latent_attention, mlp, moe,  # noqa: F401
+                     norm, parallel_mixers, retention, rope, short_conv)   # (register the built-in parts)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheBinding, ResidualStream,
                           StepContext, build_part)
 from ..parts.linear import Linear
@@ -116,6 +116,8 @@ class DecoderModel:
             resolve_pending(stream)
         f = self.final_norm.forward(stream.x, delta=stream.pending, rows=logits_rows)
         logits = self.lm_head(f, out_dtype=torch.float32)
+        if s.logit_scale != 1.0:
+            ops.scale(logits, s.logit_scale)
         if s.logit_softcap > 0:
             ops.softcap(logits, s.logit_softcap)
         return logits

@@ -33,10 +33,11 @@ class KvCacheNeed:
     window: Optional[int] = None
     block_size: Optional[int] = None
     planes: int = 2
+    keep_first: int = 0        # with a window: the first so many tokens of a request stay (their pages are not given back)
 
     def group_key(self):
         # layers whose pages live and die together: same span of tokens, same page size
-        return ("kv", self.window, self.block_size)
+        return ("kv", self.window, self.block_size, self.keep_first if self.window is not None else 0)
 
 
 @dataclass(frozen=True)
@@ -246,6 +247,13 @@ class ResidualStream:
     half: Optional["HalfNormed"] = None
     half_norm: Optional["Norm"] = None
     cast: Optional[torch.Tensor] = None
+    # for models that average over the results of all layers so far: what the embedding gave (never written again)
+    # and one buffer [runs + 1, T, h] in which run i works in place on row i and leaves the next run's input in row i + 1
+    origin: Optional[torch.Tensor] = None
+    results: Optional[torch.Tensor] = None
+    # the next block's mixer input, already normed by the kernel that last changed ``x`` (made for ``normed_by``)
+    normed: Optional[torch.Tensor] = None
+    normed_by: Optional["Norm"] = None
 
 
 class Block:

@@ -173,3 +173,111 @@ class PostNormResidual(Block):
             h = self._input(stream)
             branch = part.forward(h, ctx, cache) if part is self.mixer else part.forward(h, ctx)
             self._join(stream, branch, norm)
+
+
+@BLOCKS.register("sandwich_residual")
+class SandwichResidual(Block):
+    """``x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x)))``: every sublayer has a norm on its input and one on
+    its output, all four RMS norms whose weight is one number.  A layer may have no feed-forward (kind "none").
+
+    extras: ``depth_average`` (tensor name after the layer's prefix) and ``depth_index`` (how many layers ran before
+    this one): with X_0 what the embedding gave and X_(j+1) the result of layer j, what leaves layer i is
+    ``sum_(j=0..i+1) w[j] X_j`` with the layer's weights ``w`` [i + 2], not X_(i+1) itself.  The results live in one
+    buffer of the stream (``ResidualStream.results``): layer i works in place on row i and leaves the next layer's
+    input in row i + 1; X_0 stays where the embedding wrote it.
+
+    One kernel per sublayer joins it to the stream: the output norm, the 32-bit add, after the layer's last sublayer
+    the average, and the input norm of whatever reads the stream next (this layer's feed-forward, or the next layer's
+    mixer when that is a block of this kind with the same eps), rounded to the activation type.
+
+    extras also holds the PartSpecs of the two output norms, ``mixer_norm_out`` and ``feed_forward_norm_out``."""
+
+    def configure(self, extras, env, prefix) -> None:
+        from .base import NORMS, build_part
+        super().configure(extras, env, prefix)
+        self.mixer_norm_out = build_part(NORMS, self.extras["mixer_norm_out"], env, prefix)
+        self.feed_forward_norm_out = build_part(NORMS, self.extras["feed_forward_norm_out"], env, prefix)
+
+    def parts(self):
+        return super().parts() + [self.mixer_norm_out, self.feed_forward_norm_out]
+
+    def declare(self):
+        from .spec import TensorDecl
+        name = self.extras.get("depth_average")
+        return [TensorDecl(self.prefix + name, (int(self.extras["depth_index"]) + 2,), init="ones")] if name else []
+
+    def bind(self, tensors):
+        name = self.extras.get("depth_average")
+        self.depth_weights = tensors[self.prefix + name].contiguous() if name else None
+        self.depth_index = int(self.extras.get("depth_index", 0))
+
+    def kernel_libraries(self):
+        return ["sandwich", "norm", "elementwise"]
+
+    def _no_feed_forward(self) -> bool:
+        return bool(getattr(self.feed_forward, "absent", False))
+
+    def _gain(self, norm) -> float:
+        if not isinstance(norm, RMSNorm) or norm.gain is None:
+            raise TypeError("sandwich_residual: the norms are RMS norms whose weight is one number")
+        return norm.gain
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding,
+                next_block: Optional[Block] = None) -> None:
+        from ..kernels import ops, stream_ops
+        from .base import resolve_pending
+        if stream.half is not None:
+            raise RuntimeError("a sandwich block does not take half-normed rows")
+        if stream.pending is not None:                     # a block of another arrangement ran before this one
+            if isinstance(stream.pending, torch.Tensor):
+                ops.scaled_add(stream.x, [(stream.pending, None)])
+                stream.pending = None
+            else:
+                resolve_pending(stream)
+            stream.normed = None
+        act = self.env.act_dtype
+        T, h = stream.x.shape
+        eps = self.mixer_norm.eps
+        x_in = stream.x
+        x_work = stream.x
+        average = None
+        if self.depth_weights is not None:
+            i = self.depth_index
+            if stream.results is None:
+                if i != 0:
+                    raise RuntimeError("the average over the layers' results starts at the first layer")
+                stream.origin = stream.x
+                # a row for every layer's result and one more for what leaves the last layer
+                total = int(self.extras.get("depth_layers", 1))
+                stream.results = torch.empty((total + 1, T, h), dtype=torch.float32, device=stream.x.device)
+            if stream.results is None or i + 1 >= stream.results.shape[0]:
+                raise RuntimeError("the average over the layers' results: more layers than the first one was told of")
+            x_work = stream.results[i]
+            average = (stream.origin, stream.results, i + 1, self.depth_weights, stream.results[i + 1])
+        # the mixer's input: normed by the kernel that last changed the stream, or here
+        if stream.normed is not None and stream.normed_by is self.mixer_norm:
+            hin = stream.normed
+        else:
+            hin = self.mixer_norm.forward(x_in)
+        stream.normed = stream.normed_by = None
+        a = self.mixer.forward(hin, ctx, cache)
+        last = self._no_feed_forward()
+        nxt = next_block.mixer_norm if (isinstance(next_block, SandwichResidual) and next_block.mixer_norm.eps == eps
+                                        and next_block.mixer_norm.gain is not None) else None
+
+        def join(branch, norm, x_from, final: bool):
+            follow = nxt if final else self.feed_forward_norm
+            out = torch.empty((T, h), dtype=act, device=branch.device) if follow is not None else None
+            stream_ops.gain_norm_join(branch, self._gain(norm), eps, x_from, x_work,
+                                      average=average if final else None,
+                                      next_gain=self._gain(follow) if follow is not None else None, next_out=out)
+            return out
+
+        out = join(a, self.mixer_norm_out, x_in, last)
+        if not last:
+            f = self.feed_forward.forward(out, ctx)
+            out = join(f, self.feed_forward_norm_out, x_work, True)
+        stream.x = average[4] if average is not None else x_work
+        stream.cast = None
+        if nxt is not None:
+            stream.normed, stream.normed_by = out, nxt

@@ -37,7 +37,10 @@ class LatentAttention(Mixer):
     """params: ``num_heads``, ``nope_dim`` (D), ``rope_dim`` (P), ``v_dim``, ``kv_rank`` (R), ``q_rank``, ``scale``,
     ``eps`` (of the two latent norms), ``position`` (a PartSpec of a table rotation over the ``rope_dim`` part),
     ``own_kv`` (False: no down projection for keys and values, the entry reads another entry's cache), optional
-    ``window``, ``cache_block_size``, and the tensor names ``q_down``, ``q_norm``, ``q_up``, ``kv_down``, ``kv_norm``,
+    ``window``, ``cache_block_size``, ``sink`` (tensor name of one number per head: the softmax of head h has one more
+    term ``exp(sink_h)`` that carries no value and is not scaled), ``gate_proj`` (tensor name of ``W_g`` [H * v_dim,
+    width]: the heads' outputs are multiplied by ``sigmoid(W_g x)`` before the output projection; it rides in the
+    stacked down projection), ``out_float32``, and the tensor names ``q_down``, ``q_norm``, ``q_up``, ``kv_down``, ``kv_norm``,
     ``k_up``, ``v_up``, ``o_proj``."""
 
     def __init__(self, params, env: BuildEnv, prefix=""):
@@ -53,8 +56,14 @@ class LatentAttention(Mixer):
         self.page_size = p.get("cache_block_size")
         pos: PartSpec = p.get("position") or PartSpec("none")
         self.position = build_part(POSITION_ENCODINGS, pos, env, prefix)
-        if not self.position.fused or (self.position.fused_table() is not None and not getattr(self.position, "interleaved", False)):
-            raise ValueError("latent attention rotates pairs (2i, 2i + 1) by a table (position style 'interleaved')")
+        if not self.position.fused:
+            raise ValueError("latent attention rotates by a table (a position encoding its kernels apply)")
+        # pairs (2i, 2i + 1), or (i, i + rot / 2) for a table rotation of the other style
+        self.halves = self.position.fused_table() is not None and not getattr(self.position, "interleaved", False)
+        self.sink_name = prefix + p["sink"] if p.get("sink") else None
+        self.gate_name = prefix + p["gate_proj"] if p.get("gate_proj") else None
+        self.out_float32 = bool(p.get("out_float32", False))
+        self.sinks = None
         n = lambda key, default: prefix + p.get(key, default)
         self.names = {"dq": n("q_down", "q_down.weight"), "qn": n("q_norm", "q_norm.weight"), "uq": n("q_up", "q_up.weight"),
                       "dkv": n("kv_down", "kv_down.weight"), "kvn": n("kv_norm", "kv_norm.weight"),
@@ -71,13 +80,27 @@ class LatentAttention(Mixer):
              TensorDecl(self.names["uv"], (H * V, R)), TensorDecl(self.names["o"], (h, H * V))]
         if self.own_kv:
             d += [TensorDecl(self.names["dkv"], (R + P, h)), TensorDecl(self.names["kvn"], (R,), init="ones")]
+        if self.sink_name:
+            d.append(TensorDecl(self.sink_name, (H,)))
+        if self.gate_name:
+            d.append(TensorDecl(self.gate_name, (H * V, h)))
         return d
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         t = {k: tensors[v] for k, v in self.names.items() if v in tensors}
         rows = [t["dq"]] + ([t["dkv"]] if self.own_kv else [])
+        # the gate's rows ride behind the latents, from a multiple of 8 columns on (zero rows between)
+        self.low_width = sum(x.shape[0] for x in rows)
+        self.gate_at = (self.low_width + 7) // 8 * 8
+        if self.gate_name:
+            g = tensors[self.gate_name]
+            if self.gate_at > self.low_width:
+                rows.append(g.new_zeros((self.gate_at - self.low_width, g.shape[1])))
+            rows.append(g)
         dt = torch.float32 if any(x.dtype == torch.float32 for x in rows) else rows[0].dtype
-        self.down = Linear(torch.cat([x.to(dt) for x in rows], dim=0))           # [Rq (+ R + P), h], stacked once
+        self.down = Linear(torch.cat([x.to(dt) for x in rows], dim=0))           # [Rq (+ R + P) (+ H V), h], stacked once
+        if self.sink_name:
+            self.sinks = tensors[self.sink_name].float().contiguous()
         self.uq = Linear(t["uq"])
         self.o = Linear(t["o"])
         self.q_norm_w = t["qn"].contiguous()
@@ -91,7 +114,7 @@ class LatentAttention(Mixer):
         return KvCacheNeed(1, self.R + self.P, self.window, int(self.page_size) if self.page_size else None, planes=1)
 
     def kernel_libraries(self):
-        return (["latent_post", "attention_latent", "gemm_f32"] + self.down.kernel_libraries() + self.uq.kernel_libraries()
+        return (["latent_post", "attention_latent", "gemm_f32"] + (["elementwise"] if self.gate_name else []) + self.down.kernel_libraries() + self.uq.kernel_libraries()
                 + self.o.kernel_libraries())
 
     def forward(self, x, ctx: StepContext, cache: CacheBinding, sink=None):
@@ -99,22 +122,27 @@ class LatentAttention(Mixer):
         g = ctx.groups[cache.group]
         T = x.shape[0]
         table = self.position.fused_table()
-        low = self.down(x)                                               # [T, Rq (+ R + P)]
+        full = self.down(x)                                              # [T, Rq (+ R + P) (+ gate)]
+        low = full[:, :self.low_width]
         write = self.own_kv and cache.write
         if self.own_kv and not write:
             raise RuntimeError("a latent attention layer with its own down projection must own its cache entry")
         latent_ops.latent_down_post(low, ctx.positions, self.q_norm_w, Rq, self.kv_norm_w if write else None, R, P,
-                                    self.eps, table, cache.kv if write else None, g.slot_mapping if write else None)
+                                    self.eps, table, cache.kv if write else None, g.slot_mapping if write else None,
+                                    halves=self.halves)
         q = self.uq(low[:, :Rq])                                         # [T, H (D + P)]
         # head-major storage, seen as [T, H, *]: the batched products then write whole matrices per head
         q_lat = torch.empty((H, T, R + P), dtype=q.dtype, device=q.device).transpose(0, 1)
         self.absorb(q.view(T, H, D + P)[:, :, :D], self.uk_t, q_lat[:, :, :R])
-        latent_ops.latent_q_rope(q, ctx.positions, table, q_lat, H, D, P, R)
+        latent_ops.latent_q_rope(q, ctx.positions, table, q_lat, H, D, P, R, halves=self.halves)
         o_lat = torch.empty((H, T, R), dtype=q.dtype, device=q.device).transpose(0, 1)
         self.attend(q_lat, o_lat, cache.kv, g, ctx)
         o = torch.empty((T, H, V), dtype=q.dtype, device=q.device)
         self.absorb(o_lat, self.uv, o)
-        return self.o(o.view(T, H * V))
+        o = o.view(T, H * V)
+        if self.gate_name:
+            ops.sigmoid_gate(o, full[:, self.gate_at:self.gate_at + H * V])
+        return self.o(o, out_dtype=torch.float32 if self.out_float32 else None)
 
     # rows up to which the per-head products run on this package's own kernel (each weight read once, 32-bit
     # multiply-adds); beyond, bfloat16 goes to the library's batched product like the other prompt-sized products
@@ -134,7 +162,8 @@ class LatentAttention(Mixer):
             # inside a captured graph the longest request is whatever the engine admits
             longest = self.env.max_positions if ctx.decode_splits else ctx.max_seq_len
             latent_ops.attention_latent_tc(q_lat, o_lat, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.R, self.P,
-                                           self.scale, window, max_q_len=ctx.max_q_len, max_seq_len=longest)
+                                           self.scale, window, max_q_len=ctx.max_q_len, max_seq_len=longest,
+                                           sinks=self.sinks)
         else:
             latent_ops.attention_latent_generic(q_lat, o_lat, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.R,
-                                                self.P, self.scale, window)
+                                                self.P, self.scale, window, sinks=self.sinks)

@@ -28,13 +28,15 @@ class NoFeedForward(FeedForward):
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
     """``down( act(gate(x)) * up(x) )``.  params: ``intermediate_size``, optional ``activation`` (silu, the default;
-    gelu_tanh, relu, relu2) and tensor names ``gate_proj``, ``up_proj``, ``down_proj``."""
+    gelu_tanh, relu, relu2), ``out_float32`` (the down projection's result stays 32-bit, for an arrangement that norms
+    it before it joins the stream) and tensor names ``gate_proj``, ``up_proj``, ``down_proj``."""
 
     def __init__(self, params, env, prefix=""):
         super().__init__(params, env, prefix)
         self.hidden = env.hidden_size
         self.inter = int(params["intermediate_size"])
         self.activation = str(params.get("activation", "silu"))
+        self.out_float32 = bool(params.get("out_float32", False))
         from ..kernels.ops import GATE_ACTIVATIONS
         if self.activation not in GATE_ACTIVATIONS:
             raise ValueError(f"gated feed-forward: unknown activation {self.activation!r} ({', '.join(GATE_ACTIVATIONS)})")
@@ -70,4 +72,4 @@ class SwiGLU(FeedForward):
         act = self.gate_up.gated_pairs(x, self.activation)
         if sink is not None:                               # (residual, the norm behind this feed-forward)
             return self.down.into_residual(act, sink[0], sink[1])
-        return self.down(act)
+        return self.down(act, out_dtype=torch.float32 if self.out_float32 else None)

@@ -13,7 +13,9 @@ from .spec import TensorDecl
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """params: ``size``, ``eps``, ``weight`` (tensor name after the prefix), ``optional`` (the weight may be absent
-    from the file: the norm of a branch the layer does not have).
+    from the file: the norm of a branch the layer does not have), ``scalar`` (the weight is one number for all
+    coordinates, a tensor without dimensions: kept as ``gain``, and spread over the row for the kernels that take a
+    vector).
 
     ``out = T(v * rsqrt(mean(v^2) + eps) * w)`` with ``v = residual (+ delta)`` in 32-bit
     (crates/kernels/cuda/norm.cu:54-115, crates/layers/src/nn.rs:78-111)."""
@@ -24,13 +26,18 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.weight_name = prefix + params.get("weight", "weight")
         self.optional = bool(params.get("optional", False))
+        self.scalar = bool(params.get("scalar", False))
         self.weight: Optional[torch.Tensor] = None
+        self.gain: Optional[float] = None
 
     def declare(self) -> List[TensorDecl]:
-        return [TensorDecl(self.weight_name, (self.size,), init="ones", optional=self.optional)]
+        return [TensorDecl(self.weight_name, () if self.scalar else (self.size,), init="ones", optional=self.optional)]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         w = tensors.get(self.weight_name) if self.optional else tensors[self.weight_name]
+        if w is not None and self.scalar:
+            self.gain = float(w.float().item())
+            w = w.reshape(1).expand(self.size)
         self.weight = None if w is None else w.contiguous()
 
     def kernel_libraries(self):

@@ -57,6 +57,7 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     embedding_scale: float = 1.0        # the embedding rows are multiplied by this on their way into the residual stream
     logit_softcap: float = 0.0          # > 0: logits = cap * tanh(logits / cap)
+    logit_scale: float = 1.0            # the logits are multiplied by this (before a soft cap)
 
     def check(self) -> None:
         if not self.layers:
