@@ -1,0 +1,482 @@
+"""Sobivik on the device: every new mechanism alone against the plain implementation's function for it, then tiny
+models that differ in every size replayed whole / with a decoded tail / in portions down to two tokens / mixed on a
+pool that only holds the most demanding step, the trace runner as a process, and greedy generation through ``LLM``."""
+import json
+import math
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_sobivik as P
+import sobivik_cases as C
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+F64 = torch.float64
+
+
+def dev(t, dtype=None):
+    return t.to("cuda", dtype or t.dtype).contiguous()
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device="cuda")
+
+
+def env(h, dt, maxpos=1024):
+    from dinfer_b200.parts.base import BuildEnv
+    return BuildEnv(torch.device("cuda"), dt, h, maxpos)
+
+
+# ---------------------------------------------------------------- the join of a sublayer to the stream
+
+@pytest.mark.parametrize("a_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("h, n", [(72, 1), (256, 3), (1000, 6)])
+def test_gain_norm_join(a_dtype, h, n):
+    """Output norm, add, the average over n earlier results and the next input norm in one kernel; without the
+    average; without the next norm; in place and out of place."""
+    from dinfer_b200.kernels import stream_ops
+    g = torch.Generator().manual_seed(h + n)
+    T, eps = 7, 3e-6
+    a = torch.randn(T, h, generator=g).to(DT[a_dtype])
+    x = torch.randn(T, h, generator=g)
+    first = torch.randn(T, h, generator=g)
+    results = torch.randn(n + 1, T, h, generator=g)
+    w = torch.randn(n + 1, generator=g).to(torch.bfloat16)
+    x_new = x.double() + P.gain_norm(a.double(), torch.tensor(0.7), eps)
+    y = w[0].double() * first.double() + sum(w[j].double() * results[j - 1].double() for j in range(1, n)) + w[n].double() * x_new
+    for average in (True, False):
+        for nxt in (True, False):
+            res = dev(results)
+            x_out = res[n - 1] if average else dev(x)
+            out = torch.empty(T, h, dtype=torch.bfloat16, device="cuda") if nxt else None
+            stream_ops.gain_norm_join(dev(a), 0.7, eps, dev(x), x_out,
+                                      average=(dev(first), res, n, dev(w), res[n]) if average else None,
+                                      next_gain=1.3 if nxt else None, next_out=out)
+            assert torch.allclose(x_out.double().cpu(), x_new, atol=1e-5, rtol=1e-5)
+            z = x_new
+            if average:
+                assert torch.allclose(res[n].double().cpu(), y, atol=2e-5, rtol=1e-5)
+                z = y
+            if nxt:
+                assert torch.allclose(out.double().cpu(), P.gain_norm(z, torch.tensor(1.3), eps), atol=2e-2, rtol=2e-2)
+
+
+# ---------------------------------------------------------------- mixers alone, through the parts
+
+class Bench:
+    """One mixer part with a cache and state of its own, stepped like the engine steps it: requests come with
+    (history, new) token counts; ``run`` feeds the given portions as one batch and returns the mixer's output rows."""
+
+    def __init__(self, kind, params, W, dtype, width, block_size=16, num_blocks=64, slots=6):
+        import dinfer_b200.models.decoder  # noqa: F401  registers the parts
+        from dinfer_b200.cache.manager import CacheManager, GroupSpec
+        from dinfer_b200.engine.batch import PlanBuilder
+        from dinfer_b200.parts.base import MIXERS, CacheBinding, split_needs
+        self.dt = DT[dtype]
+        self.part = MIXERS.get(kind)(params, env(width, self.dt), "")
+        names = {d.name for d in self.part.declare()}
+        assert names == set(W), (sorted(names), sorted(W))
+        self.part.bind({k: dev(v, self.dt) for k, v in W.items()})
+        kv, st = split_needs(self.part.cache_need())
+        group = GroupSpec(window=kv.window, keep_first=kv.keep_first) if kv is not None else GroupSpec()
+        self.m = CacheManager([group], block_size, num_blocks, slots)
+        self.binding = CacheBinding(group=0)
+        if kv is not None:
+            self.binding.kv = torch.full((num_blocks, kv.planes, kv.num_kv_heads, block_size, kv.head_dim), float("nan"),
+                                         dtype=self.dt, device="cuda")
+        if st is not None:
+            self.binding.state = torch.full((slots + 1,) + tuple(st.shape), float("nan"), dtype=st.dtype, device="cuda")
+        self.pb = PlanBuilder(self.m, "cuda", 4096, 16, 64, spare_state_slot=slots)
+
+    def run(self, portions):
+        """portions = [(request, rows [n, width])]: one step."""
+        from dinfer_b200.engine.batch import StepEntry
+        entries, starts = [], []
+        for r, rows in portions:
+            start = self.m.num_computed(r) if r in self.m else 0
+            assert self.m.allocate(r, start + rows.shape[0])
+            entries.append(StepEntry(r, [0] * rows.shape[0], []))
+            starts.append(start)
+        _, _, ctx = self.pb.build(entries, starts)
+        out = self.part.forward(dev(torch.cat([rows for _, rows in portions]), self.dt), ctx, self.binding)
+        for e, s in zip(entries, starts):
+            self.m.advance(e.req_id, s + len(e.tokens))
+        return out.double().cpu()
+
+    def finish(self, r):
+        self.m.free(r)
+
+
+def cut(rows, sizes):
+    out, at = [], 0
+    for n in sizes:
+        out.append(rows[at:at + n])
+        at += n
+    assert at == rows.shape[0]
+    return out
+
+
+def run_cut(bench, inputs, plan):
+    """inputs {request: rows}; plan: a list of steps, each {request: tokens of this step}.  Returns {request: output}."""
+    at = {r: 0 for r in inputs}
+    got = {r: [] for r in inputs}
+    for step in plan:
+        portions = [(r, inputs[r][at[r]:at[r] + n]) for r, n in step.items()]
+        out = bench.run(portions)
+        o = 0
+        for r, n in step.items():
+            got[r].append(out[o:o + n])
+            o += n
+            at[r] += n
+            if at[r] == inputs[r].shape[0]:
+                bench.finish(r)
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+PLAN = [{"a": 40, "b": 1}, {"b": 1, "c": 2}, {"a": 1, "c": 2, "d": 70}, {"a": 1, "b": 3, "c": 1}, {"a": 30, "e": 1},
+        {"a": 2, "b": 2, "e": 1}, {"a": 1, "e": 1}, {"a": 1, "f": 25}, {"f": 1}, {"f": 1}, {"f": 64}]
+LENS = {"a": 76, "b": 7, "c": 5, "d": 70, "e": 3, "f": 91}
+
+
+def rows_for(width, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return {r: torch.randn(n, width, generator=g).to(DT[dtype]).float() for r, n in LENS.items()}
+
+
+def weights_for(decls, dtype, seed, std=0.1, scale=None):
+    g = torch.Generator().manual_seed(seed)
+    W = {}
+    for d in decls:
+        t = torch.randn(d.shape, generator=g) * std
+        for suffix, f in (scale or {}).items():
+            if d.name.endswith(suffix):
+                t = t * f
+        W[d.name] = t.to(torch.bfloat16).float()            # the same values in every dtype
+    return W
+
+
+def close(got, want, dtype, what=""):
+    tol = 2e-5 if dtype == "float32" else 6e-2
+    scale = float(want.abs().max())
+    err = float((got - want).abs().max()) / max(scale, 1e-9)
+    assert err <= tol, f"{what}: {err}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps, width", [(1, 40), (2, 64), (3, 72), (6, 100)])
+def test_short_conv_input(dtype, taps, width):
+    """Portions of one and two tokens, requests that sit steps out, slots that another request held before; the
+    mixer inside is a plain product so that only the convolution shows."""
+    from dinfer_b200.parts.base import MIXERS, Mixer
+    from dinfer_b200.parts.spec import PartSpec
+
+    class Passes(Mixer):
+        def forward(self, x, ctx, cache):
+            return x
+    MIXERS.register("passes_for_test", Passes, replace=True)
+    try:
+        W = {"conv": (torch.randn(width, taps, generator=torch.Generator().manual_seed(taps)) * 0.5).to(torch.bfloat16).float()}
+        bench = Bench("short_conv_input", {"inner": PartSpec("passes_for_test"), "taps": taps, "weight": "conv"}, W, dtype, width,
+                      slots=4)
+        inputs = rows_for(width, dtype, 3)
+        got = run_cut(bench, inputs, PLAN)
+        for r, x in inputs.items():
+            want, _ = P.short_conv_input(x.double(), W["conv"], torch.zeros(taps - 1, width, dtype=F64))
+            close(got[r], want, dtype, r)
+    finally:
+        MIXERS.unregister("passes_for_test")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H_, dk, dv, width", [(2, 16, 24, 64), (3, 128, 40, 96), (1, 12, 20, 72), (4, 64, 64, 128), (5, 33, 7, 40),
+                                               (2, 256, 96, 64)])
+def test_retention(dtype, H_, dk, dv, width):
+    """The part against the recurrence written out token by token: batches of unequal requests, portions of one and
+    two tokens and of more than a chunk, state rows that another request held before."""
+    decay = [1.0 - 0.3 ** (i + 1) for i in range(H_)]
+    p = {"num_heads": H_, "key_dim": dk, "value_dim": dv, "decay": decay, "eps": 1e-5}
+    import dinfer_b200.models.decoder  # noqa: F401
+    from dinfer_b200.parts.base import MIXERS
+    W = weights_for(MIXERS.get("retention")(p, env(width, torch.float32), "mix.").declare(), dtype, dk, std=0.15)
+    bench = Bench("retention", dict(p, q_proj="mix.q", k_proj="mix.k", v_proj="mix.v", gate_proj="mix.g", o_proj="mix.o"), W,
+                  dtype, width, slots=4)
+    inputs = rows_for(width, dtype, 11)
+    got = run_cut(bench, inputs, PLAN)
+    m = {"heads": H_, "dim": dk, "vdim": dv, "decay": decay}
+    for r, x in inputs.items():
+        want = P.retention(x.double(), {k: v for k, v in W.items()}, m, {"S": torch.zeros(H_, dk, dv, dtype=F64)}, 1e-5)
+        close(got[r], want, dtype, r)
+
+
+def test_retention_remembers_a_far_token():
+    """A head that hardly decays: a value written at the first token is read back 300 tokens later, through
+    portions, with a query that only the first key answers."""
+    from dinfer_b200.kernels import stream_ops
+    T, dk, dv = 301, 16, 8
+    q, k, v = torch.zeros(T, dk), torch.zeros(T, dk), torch.randn(T, dv, generator=torch.Generator().manual_seed(1))
+    k[0, 3] = 1.0
+    k[1:, 5] = 1.0                                           # every later key lies across the first
+    q[T - 1, 3] = 1.0
+    state = torch.full((3, dk * dv + 5), float("nan"), device="cuda")
+    decay = torch.tensor([0.999], device="cuda")
+    at, outs = 0, []
+    for n in (1, 2, 40, 33, 1, 1, 200, 22, 1):
+        o = stream_ops.retention(dev(q[at:at + n]), dev(k[at:at + n]), dev(v[at:at + n]), decay, state, i32([0, n]), i32([1]),
+                                 i32([1 if at == 0 else 0]), 1, dk, dv, 1.0)
+        outs.append(o.cpu())
+        at += n
+    got = torch.cat(outs)[T - 1, 0]
+    assert torch.allclose(got, v[0] * 0.999 ** 300, atol=1e-6, rtol=1e-5)
+    assert torch.isnan(state[1, dk * dv:]).all() and torch.isnan(state[0]).all()      # nothing beside its own row
+
+
+def test_ramp_rotation_table():
+    from dinfer_b200.parts.rope import rope_table
+    for dims, base, sc in ((8, 500.0, (4.0, 64, 8.0, 2.0)), (32, 1e6, (2.0, 2048, 32.0, 1.0)), (6, 100.0, (2.5, 40, 16.0, 1.0)),
+                           (64, 5000.0, None)):
+        rot = {"dims": dims, "base": base}
+        if sc:
+            rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), sc))
+        cos, sin = P.yarn_angles(rot, torch.arange(700))
+        t = rope_table(dims, base, 700, "cuda", ramp=sc).cpu().double()
+        assert torch.allclose(t[:, :dims // 2], cos, atol=1e-6) and torch.allclose(t[:, dims // 2:], sin, atol=1e-6)
+
+
+LATENT = [(3, 8, 8, 12, 24, 20, 20, 8, 16), (4, 16, 16, 40, 32, 48, 50, 16, 16), (5, 6, 10, 14, 18, 7, 33, 6, 4),
+          (8, 64, 64, 64, 128, 96, 100, 64, 64), (2, 16, 32, 16, 64, 24, 1, 32, 8)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H_, D, Pr, V, R, Rq, window, rot, block_size", LATENT)
+def test_latent_attention_window_sink_gate(dtype, H_, D, Pr, V, R, Rq, window, rot, block_size):
+    """Prompts, portions behind a history and decoded tokens in one batch: rotation in halves with stretched
+    frequencies, the window's edge, a sink per head (large ones, so that leaving it out shows) and the output gate."""
+    from dinfer_b200.parts.base import MIXERS
+    from dinfer_b200.parts.spec import PartSpec
+    import dinfer_b200.models.decoder  # noqa: F401
+    width = 64
+    sc = {"factor": 3.0, "original": 48, "fast": 8.0, "slow": 1.5}
+    names = dict(q_down="mix.dq", q_norm="mix.dq.norm", q_up="mix.uq", kv_down="mix.dkv", kv_norm="mix.dkv.norm", k_up="mix.uk",
+                 v_up="mix.uv", o_proj="mix.o", sink="mix.sink", gate_proj="mix.g")
+    p = dict(names, num_heads=H_, nope_dim=D, rope_dim=Pr, v_dim=V, kv_rank=R, q_rank=Rq, scale=0.4, eps=1e-5, window=window,
+             position=PartSpec("rope", {"head_dim": Pr, "rotary_dim": rot, "theta": 300.0, "max_positions": 1024, "style": "neox",
+                                        "ramp": sc}))
+    W = weights_for(MIXERS.get("latent_attention")(p, env(width, torch.float32), "").declare(), dtype, H_ + D, std=0.2,
+                    scale={"mix.sink": 15.0, "mix.uq": 3.0})
+    for k in ("mix.dq.norm", "mix.dkv.norm"):
+        W[k] = (W[k] + 1.0).to(torch.bfloat16).float()
+    bench = Bench("latent_attention", p, W, dtype, width, block_size=block_size, num_blocks=512 // block_size)
+    inputs = rows_for(width, dtype, 5)
+    got = run_cut(bench, inputs, PLAN)
+    m = {"heads": H_, "dim": D, "rot_dim": Pr, "vdim": V, "kv_rank": R, "q_rank": Rq, "scale": 0.4, "mask": {"size": window},
+         "rot": {"base": 300.0, "dims": rot, "scaling": sc}}
+    for r, x in inputs.items():
+        want = P.latent_attention(x.double(), W, m, {"c": torch.zeros(0, R, dtype=F64), "kr": torch.zeros(0, Pr, dtype=F64)}, 1e-5)
+        close(got[r], want, dtype, r)
+
+
+DIFF = [(4, 2, 8, 16, 9, 3, 16), (6, 1, 24, 40, 7, 0, 16), (3, 3, 10, 6, 1, 5, 4), (9, 3, 6, 14, 40, 17, 8), (4, 2, 64, 128, 64, 4, 64),
+        (2, 2, 32, 32, 200, 70, 16)]
+
+
+def diff_case(dtype, H_, G, D, V, window, keep, block_size, inputs=None, tie=False, width=64, plan=PLAN, seed=0):
+    from dinfer_b200.parts.base import MIXERS
+    import dinfer_b200.models.decoder  # noqa: F401
+    names = dict(q_proj="mix.q", k_proj="mix.k", v_proj="mix.v", gate_proj="mix.g", o_proj="mix.o", lambda_q1="mix.lq1",
+                 lambda_k1="mix.lk1", lambda_q2="mix.lq2", lambda_k2="mix.lk2")
+    p = dict(names, num_heads=H_, num_kv_heads=G, head_dim=D, v_dim=V, scale=0.5, diff=0.35, eps=1e-5, window=window, keep_first=keep)
+    W = weights_for(MIXERS.get("differential_attention")(p, env(width, torch.float32), "").declare(), dtype, H_ * D + seed, std=0.2,
+                    scale={"lq1": 4.0, "lk1": 4.0, "lq2": 4.0, "lk2": 4.0})
+    if tie:                                                  # a key made of a token answers the query made of the same token
+        W["mix.k"] = W["mix.q"].view(G, H_ // G, 2 * D, width)[:, 0].reshape(G * 2 * D, width).clone()
+    bench = Bench("differential_attention", p, W, dtype, width, block_size=block_size, num_blocks=512 // block_size)
+    inputs = inputs if inputs is not None else rows_for(width, dtype, 9)
+    got = run_cut(bench, inputs, plan)
+    m = {"heads": H_, "kv_heads": G, "dim": D, "vdim": V, "scale": 0.5, "diff": 0.35, "mask": {"size": window, "keep_first": keep}}
+    want = {r: P.differential_attention(x.double(), W, m, {"k": torch.zeros(0, G, 2, D, dtype=F64), "v": torch.zeros(0, G, V, dtype=F64)},
+                                        1e-5) for r, x in inputs.items()}
+    return got, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H_, G, D, V, window, keep, block_size", DIFF)
+def test_differential_attention(dtype, H_, G, D, V, window, keep, block_size):
+    got, want = diff_case(dtype, H_, G, D, V, window, keep, block_size)
+    for r in want:
+        close(got[r], want[r], dtype, r)
+
+
+@pytest.mark.parametrize("new", [1, 6])
+@pytest.mark.parametrize("where", ["window_in", "window_out", "kept_in", "kept_out"])
+def test_differential_attention_keys_at_the_edges(new, where):
+    """One key made to dominate (its token's row is a multiple of the query token's and keys are tied to queries):
+    just inside and just outside the window, the last kept first token and the one behind it, for the last token of
+    a prompt portion and for a decoded one.  Outside it must leave no trace; pages of 4 put the kept tokens on
+    pages the window has long passed."""
+    window, keep, hist = 24, 6, 61
+    q_at = hist + new - 1
+    k_at = {"window_in": q_at - window + 1, "window_out": q_at - window, "kept_in": keep - 1, "kept_out": keep}[where]
+    g = torch.Generator().manual_seed(3)
+    rows = {"a": torch.randn(hist + new, 64, generator=g).to(torch.bfloat16).float(),
+            "b": torch.randn(33, 64, generator=g).to(torch.bfloat16).float()}
+    plain = {k: v.clone() for k, v in rows.items()}
+    rows["a"][k_at] = rows["a"][q_at] * 3.0
+    plan = [{"a": hist, "b": 31}, {"a": new, "b": 2}]
+    got, want = diff_case("float32", 4, 2, 16, 24, window, keep, 4, inputs=rows, tie=True, plan=plan)
+    close(got["a"], want["a"], "float32")
+    base, _ = diff_case("float32", 4, 2, 16, 24, window, keep, 4, inputs=plain, tie=True, plan=plan)
+    moved = float((got["a"][q_at] - base["a"][q_at]).abs().max())
+    assert (moved > 1e-2) == where.endswith("_in"), moved
+
+
+# ---------------------------------------------------------------- whole models
+
+LENGTHS = {"A": {"a": 1, "b": 2, "c": 45, "d": 131, "e": 77},
+           "B": {"a": 150, "b": 3, "c": 66, "d": 1, "e": 19},
+           "C": {"a": 97, "b": 40, "c": 2, "d": 71},
+           "D": {"a": 120, "b": 1, "c": 33, "d": 64},
+           "E": {"a": 190, "b": 17, "c": 65, "d": 128}}
+BF16_WORST, BF16_RMS = 0.3, 0.08
+
+
+def rms_err(got, want):
+    if not np.isfinite(got).all():
+        return float("inf")
+    return float(np.sqrt(np.mean((got.astype(np.float64) - want) ** 2) / np.mean(np.asarray(want) ** 2)))
+
+
+class Oracle:
+    def __init__(self, model_dir):
+        self.cfg = json.load(open(os.path.join(model_dir, "config.json")))
+        self.W = C.load_weights(model_dir)
+        self._cache = {}
+
+    def logits(self, ids):
+        key = tuple(ids)
+        if key not in self._cache:
+            self._cache[key] = P.forward(self.cfg, self.W, list(ids), P.new_state(self.cfg)).numpy()
+        return self._cache[key]
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    out = {}
+    for name, cfg in C.CONFIGS.items():
+        for dt in DT:
+            out[(name, dt)] = C.write_model(str(tmp_path_factory.mktemp(f"sobivik{name}_{dt}")), cfg, 11 + ord(name), DT[dt])
+    return out
+
+
+_REQUESTS = {}
+
+
+def requests(name, model_dirs):
+    if name not in _REQUESTS:
+        cfg, rng = C.CONFIGS[name], random.Random(7 + ord(name))
+        oracle = Oracle(model_dirs[(name, "bfloat16")])
+        tokens = {r: H.random_tokens(rng, n, cfg["vocab"]) for r, n in LENGTHS[name].items()}
+        _REQUESTS[name] = (tokens, {r: oracle.logits(t) for r, t in tokens.items()})
+    return _REQUESTS[name]
+
+
+def test_plain_in_pieces_is_plain_whole(model_dirs):
+    """The plain implementation fed in pieces (its carried state) gives what it gives in one piece."""
+    for name in ("A", "C"):
+        oracle = Oracle(model_dirs[(name, "float32")])
+        ids = H.random_tokens(random.Random(1), 60, oracle.cfg["vocab"])
+        whole = oracle.logits(ids)
+        state, parts, at = P.new_state(oracle.cfg), [], 0
+        for n in (1, 2, 30, 1, 26):
+            parts.append(P.forward(oracle.cfg, oracle.W, ids[at:at + n], state).numpy())
+            at += n
+        assert np.allclose(np.concatenate(parts), whole, atol=1e-9, rtol=1e-9)
+
+
+@pytest.mark.parametrize("block_size", [4, 16, 64])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(C.CONFIGS))
+def test_replay_all_ways(model_dirs, name, dtype, block_size):
+    """Every position of every request: whole / with a decoded tail long enough to pass page borders and windows /
+    in portions down to two tokens / mixed with up to four live requests (some sitting steps out) on a pool and with
+    state slots that only hold the most demanding step, so that pages and slots are freed and used again."""
+    model_dir = model_dirs[(name, dtype)]
+    rng = random.Random(99 + ord(name))
+    lengths = LENGTHS[name]
+    tokens, want = requests(name, model_dirs)
+    schedules = {
+        "whole": H.schedule_whole(lengths),
+        "tail": H.schedule_tail(lengths, 70),
+        "chunks": H.schedule_chunks(lengths, rng),
+        "mixed": H.schedule_mixed(lengths, rng),
+        "mixed2": H.schedule_mixed(dict(reversed(list(lengths.items()))), rng, max_live=3, decode_tail=40),
+    }
+    max_tokens = max(H.max_live_tokens(s, round_to=max(64, block_size)) for s in schedules.values())
+    rp = H.LocalReplay(model_dir, dtype, max_tokens, block_size=block_size)
+    worst, spread = {}, {}
+    for sname, steps in schedules.items():
+        got = H.run_schedule(rp, steps, tokens, tag=sname + "/")
+        worst[sname] = max(H.rel_err(got[r], want[r]) for r in tokens)
+        spread[sname] = max(rms_err(got[r], want[r]) for r in tokens)
+    assert rp.close() == 0
+    # 32-bit is the sharp test.  In bfloat16 a rounding can travel far in this design (every sublayer's output is
+    # normed back to unit size, its relative error included), so there the root mean square of the differences over a
+    # request is held to BF16_RMS of the logits' own and the largest single difference to BF16_WORST of their largest
+    # (a fault gives about 1).
+    if dtype == "float32":
+        bad = {k: v for k, v in worst.items() if not v <= H.TOLERANCE[dtype]}
+    else:
+        bad = {k: (worst[k], spread[k]) for k in worst if not (worst[k] <= BF16_WORST and spread[k] <= BF16_RMS)}
+    assert not bad, f"{name} {dtype} pages of {block_size}: {bad} (largest: {worst}; rms: {spread})"
+
+
+def test_trace_runner_and_first_tokens(model_dirs, tmp_path):
+    """Through ``bin/trace_run`` as a process: the first tokens of sequences (a request of one token, the first two
+    positions of others), and a request that sits steps out while others come and go."""
+    model_dir = model_dirs[("A", "float32")]
+    cfg = C.CONFIGS["A"]
+    rng = random.Random(5)
+    tokens = {r: H.random_tokens(rng, n, cfg["vocab"]) for r, n in {"p": 1, "q": 2, "r": 70, "s": 45}.items()}
+    oracle = Oracle(model_dir)
+    rp = H.Replay(model_dir, "float32", str(tmp_path / "out"), 256)
+    try:
+        a = rp.step([{"id": "p", "tokens": tokens["p"], "want": [0]}, {"id": "r", "tokens": tokens["r"][:2], "want": [0, 1]}], ["p"])
+        b = rp.step([{"id": "q", "tokens": tokens["q"], "want": [0, 1]}, {"id": "s", "tokens": tokens["s"][:40], "want": [39]}], ["q"])
+        c = rp.step([{"id": "r", "tokens": tokens["r"][2:], "want": [67]}, {"id": "s", "tokens": tokens["s"][40:41], "want": [0]}], ["r"])
+        d = rp.step([{"id": "s", "tokens": tokens["s"][41:], "want": [3]}], ["s"])
+    finally:
+        assert rp.close() == 0
+    for got, want in ((a[0], oracle.logits(tokens["p"])[0]), (a[1:], oracle.logits(tokens["r"])[:2]),
+                      (b[:2], oracle.logits(tokens["q"])), (b[2], oracle.logits(tokens["s"])[39]),
+                      (c[0], oracle.logits(tokens["r"])[69]), (c[1], oracle.logits(tokens["s"])[40]),
+                      (d[0], oracle.logits(tokens["s"])[44])):
+        assert H.rel_err(np.asarray(got), np.asarray(want)) <= H.TOLERANCE["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "E"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
+    """``LLM.generate``: scheduler, chunked prompts (a token budget below the prompts' lengths), decode steps replayed
+    as CUDA graphs (the mixers' state is driven from device tensors), greedy sampling; more requests than run at once;
+    decoding long enough to pass the windows."""
+    from dinfer_b200 import LLM, SamplingParams
+    model_dir = model_dirs[(name, dtype)]
+    cfg = C.CONFIGS[name]
+    rng = random.Random(21)
+    prompts = [H.random_tokens(rng, n, cfg["vocab"]) for n in (1, 5, 23, 40, 9, 31)]
+    llm = LLM(model_dir, dtype=dtype, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=16, block_size=16,
+              num_blocks=48)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=80, ignore_eos=True))
+    oracle = Oracle(model_dir)
+    exact = total = 0
+    for p, o in zip(prompts, outs):
+        assert len(o.output_ids) == 80
+        lg = oracle.logits(list(p) + list(o.output_ids))
+        exact += sum(int(lg[len(p) - 1 + i].argmax()) == t for i, t in enumerate(o.output_ids))
+        total += 80
+    assert exact >= (0.9 if dtype == "bfloat16" else 0.99) * total, (exact, total)
+    assert any(isinstance(k, int) for k in llm.runner._graphs)
