@@ -378,7 +378,33 @@ ZASIPEL_SIZES = {
     "medium": (_zasipel_cfg(2048, 16, 4, 128, 1024, 16, 8, 64, 6, 1408, 2816), _qwen3_cfg(2048, 16, 4, 128, 7680)),
     "large": (_zasipel_cfg(4096, 32, 8, 128, 1024, 32, 16, 64, 6, 2048, 4096), _qwen3_cfg(4096, 32, 8, 128, 12288)),
 }
-DESIGNS = {"dobedra": DESIGN_SIZES, "zasipel": ZASIPEL_SIZES}
+
+
+# ---------------------------------------------------------------- Sobivik beside Qwen3 at equal layer sizes
+def _sobivik_cfg(width, heads, kv_heads, dim, kv_rank, q_rank, window, ff, vocab=32768):
+    decay = [1.0 - 2.0 ** (-5.0 - 6.0 * i / max(1, heads - 1)) for i in range(heads)]
+    ret = {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}}
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": kv_rank, "q_rank": q_rank,
+                     "scale": (1.5 * dim) ** -0.5, "mask": {"size": window},
+                     "rot": {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    dif = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5,
+                     "diff": 0.5, "mask": {"size": window, "keep_first": 4}}}
+    mlp = {"kind": "dense", "ff": ff}
+    return {"architecture": "Sobivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "canon": {"taps": 4}, "layers": [dict(l, mlp=mlp) for l in (ret, lat, dif, ret)]}
+
+
+# four layers (retention, latent attention over a window, differential attention over a window with kept first tokens,
+# retention), heads of 64 or 128 (each differential map half a head), a window of 1024, a convolution of four taps on
+# every mixer's input, the dense feed-forward of the Qwen3 layers beside them
+SOBIVIK_SIZES = {
+    "small": (_sobivik_cfg(1024, 16, 4, 64, 256, 512, 1024, 2048), _qwen3_cfg(1024, 16, 4, 64, 2048)),
+    "medium": (_sobivik_cfg(2048, 16, 4, 128, 512, 1536, 1024, 7680), _qwen3_cfg(2048, 16, 4, 128, 7680)),
+    "large": (_sobivik_cfg(4096, 32, 8, 128, 512, 1536, 1024, 12288), _qwen3_cfg(4096, 32, 8, 128, 12288)),
+}
+DESIGNS = {"dobedra": DESIGN_SIZES, "zasipel": ZASIPEL_SIZES, "sobivik": SOBIVIK_SIZES}
 
 
 def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None):
@@ -440,7 +466,7 @@ def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None
 
 
 def design_run(a) -> int:
-    """``--design dobedra|zasipel``: prefill and decode throughput of four layers of the design beside four Qwen3 layers
+    """``--design dobedra|zasipel|sobivik``: prefill and decode throughput of four layers of the design beside four Qwen3 layers
     of the same width and head count, at the sizes of ``DESIGNS``; one JSON line."""
     rows = {}
     table = DESIGNS[a.design]
@@ -483,11 +509,11 @@ def main() -> int:
     ap.add_argument("--closed-loop", default=None, metavar="C,P,O",
                     help="the reference's serving measurement at engine level instead: C clients, each sending its "
                          "next request when the last has ended, prompts of P tokens, O generated tokens (--shape applies)")
-    ap.add_argument("--design", choices=["dobedra", "zasipel"], default=None,
+    ap.add_argument("--design", choices=["dobedra", "zasipel", "sobivik"], default=None,
                     help="instead of the benchmark: four layers of this design beside four Qwen3 layers of equal width, "
                          "prefill and decode, at a few layer sizes")
     ap.add_argument("--design-size", choices=["small", "medium", "large"], default=None, help="only this size")
-    ap.add_argument("--design-model", choices=["dobedra", "zasipel", "qwen3"], default=None, help="with --profile: which of the two")
+    ap.add_argument("--design-model", choices=["dobedra", "zasipel", "sobivik", "qwen3"], default=None, help="with --profile: which of the two")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -45,6 +45,7 @@ LIBRARIES: Dict[str, tuple] = {
     "retention": ("retention.cu", []),
     "short_conv": ("short_conv.cu", []),
     "attention_diff": ("attention_diff.cu", []),
+    "attention_diff_tc": ("attention_diff_tc.cu", []),
     "sandwich": ("sandwich.cu", []),
     # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
     "host_core": ("host_core.cpp", []),

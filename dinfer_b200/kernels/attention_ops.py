@@ -244,3 +244,49 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_
                  float(scale), int(window), int(bool(sink)), int(max_q_len), int(any_decode), int(any_prefill), int(splits),
                  ptr(scratch if splits > 1 else None), stream_handle()), "attention_tc")
     return out
+
+
+def diff_tc_supported(dtype: torch.dtype, head_dim: int, v_dim: int, group: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (32, 64, 128) and v_dim in (64, 128) and 1 <= group <= 16
+
+
+def attention_diff_tc(q: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], cache: torch.Tensor,
+                      block_table: torch.Tensor, cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, v_dim: int, scale: float, window: int, keep_first: int,
+                      lam: float, eps: float, out_scale: float, max_q_len: int, any_decode: bool, any_prefill: bool,
+                      splits: int) -> torch.Tensor:
+    """Differential attention over the paged cache on the tensor cores (bfloat16): per head two softmax maps (queries
+    and keys ``[map 1 | map 2]``, ``head_dim`` each) over the same values, ``o = a1 - lam * a2``, then ``o / rms(o) *
+    out_scale * sigmoid(gate[t, h])``.  A query at p sees j <= p with p - j < window or j < keep_first.  ``q`` [T, H * 2 D]
+    and ``gate`` [T, H] may be strided views of one projection's rows; cache rows are ``max(2 D, v_dim)`` wide."""
+    require_cuda(q, out, gate, cache, block_table, cu_seqlens, seq_lens)
+    T = q.shape[0]
+    B = cu_seqlens.numel() - 1
+    row = max(2 * head_dim, v_dim)
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
+            or (gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(1) != 1 or tuple(gate.shape) != (T, num_heads))):
+        raise KernelError("attention_diff_tc: bfloat16 only, gate [T, H]")
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention_diff_tc: contiguous last axes and a contiguous cache")
+    if q.shape[1] != num_heads * 2 * head_dim or tuple(out.shape) != (T, num_heads * v_dim):
+        raise KernelError("attention_diff_tc: q [T, H * 2 D], out [T, H * Dv]")
+    for t, n in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (seq_lens, "seq_lens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"attention_diff_tc: {n} must be contiguous int32")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != row:
+        raise KernelError(f"attention_diff_tc: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, {row}]")
+    if not any_decode:
+        splits = 1
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(B * num_heads * 2 * splits * (v_dim + 2), dtype=torch.float32, device=q.device)
+    lib, f = _fn("attention_diff_tc", "dinfer_attention_diff_tc",
+                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_float,
+                  c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
+                 ptr(cache), ptr(block_table), block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), B, num_heads,
+                 num_kv_heads, head_dim, v_dim, row, cache.shape[3], float(scale), int(window or 0), int(keep_first or 0),
+                 float(lam), float(eps), float(out_scale), int(max_q_len), int(bool(any_decode)), int(bool(any_prefill)),
+                 int(splits), ptr(scratch), stream_handle()), "attention_diff_tc")
+    return out

@@ -11,7 +11,10 @@ per head and token.  No position encoding.  A query at position p sees the keys 
 Data flow of one step:
   [q | k | v | gate] = x [W_q; W_k; W_v; W_g]^T     one stacked product
   k, v -> cache                                      rows [map 1 | map 2] and values, ``max(2 D, Dv)`` wide
-  o = attention_diff(q, cache, gate)                 both maps, the difference, the norm and the gate in one kernel
+  o = attention_diff(q, cache, gate)                 both maps, the difference, the norm and the gate in one kernel:
+                                                     on the tensor cores in bfloat16 where it takes the sizes (prompt
+                                                     portions in tiles of rows, decoded tokens with the keys split),
+                                                     else the plain-arithmetic kernel, which takes every size
   y = o W_o^T
 """
 from __future__ import annotations
@@ -21,7 +24,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import attention_ops, ops
 from .base import MIXERS, BuildEnv, CacheBinding, KvCacheNeed, Mixer, StepContext
 from .linear import Linear
 from .spec import TensorDecl
@@ -81,7 +84,7 @@ class DifferentialAttention(Mixer):
                            keep_first=self.keep_first)
 
     def kernel_libraries(self):
-        return ["qk_post", "attention_diff"] + self.proj.kernel_libraries() + self.o.kernel_libraries()
+        return ["qk_post", "attention_diff", "attention_diff_tc"] + self.proj.kernel_libraries() + self.o.kernel_libraries()
 
     def forward(self, x, ctx: StepContext, cache: CacheBinding):
         H, G, D, Dv = self.H, self.Hkv, self.D, self.Dv
@@ -93,7 +96,15 @@ class DifferentialAttention(Mixer):
             ops.qkv_post_general(P[:, :nq + nk + nv], ctx.positions, H, G, 2 * D, Dv, self.eps, None, None, False, True, None,
                                  cache.kv, g.slot_mapping, g.block_size)
         out = torch.empty((P.shape[0], H * Dv), dtype=P.dtype, device=P.device)
-        ops.attention_diff(P[:, :nq], out, P[:, nq + nk + nv:nq + nk + nv + H], cache.kv, g.block_table, ctx.cu_seqlens,
-                           ctx.positions, H, G, D, Dv, self.scale, int(self.window or 0), self.keep_first, self.lam,
-                           self.eps, 1.0 - self.diff)
+        q, gate, window = P[:, :nq], P[:, nq + nk + nv:nq + nk + nv + H], int(self.window or 0)
+        if attention_ops.diff_tc_supported(P.dtype, D, Dv, H // G):
+            # the keys a decoded token sees end at the window (and the kept first ones): no more splits than they fill
+            seen = min(ctx.max_seq_len, window + self.keep_first) if window else ctx.max_seq_len
+            splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, G, seen)
+            attention_ops.attention_diff_tc(q, out, gate, cache.kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, H, G, D, Dv,
+                                            self.scale, window, self.keep_first, self.lam, self.eps, 1.0 - self.diff,
+                                            ctx.max_q_len, ctx.any_decode, ctx.any_prefill, splits)
+        else:
+            ops.attention_diff(q, out, gate, cache.kv, g.block_table, ctx.cu_seqlens, ctx.positions, H, G, D, Dv,
+                               self.scale, window, self.keep_first, self.lam, self.eps, 1.0 - self.diff)
         return self.o(out, out_dtype=torch.float32 if self.out_float32 else None)

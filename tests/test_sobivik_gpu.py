@@ -72,12 +72,13 @@ class Bench:
     """One mixer part with a cache and state of its own, stepped like the engine steps it: requests come with
     (history, new) token counts; ``run`` feeds the given portions as one batch and returns the mixer's output rows."""
 
-    def __init__(self, kind, params, W, dtype, width, block_size=16, num_blocks=64, slots=6):
+    def __init__(self, kind, params, W, dtype, width, block_size=16, num_blocks=64, slots=6, splits=0):
         import dinfer_b200.models.decoder  # noqa: F401  registers the parts
         from dinfer_b200.cache.manager import CacheManager, GroupSpec
         from dinfer_b200.engine.batch import PlanBuilder
         from dinfer_b200.parts.base import MIXERS, CacheBinding, split_needs
         self.dt = DT[dtype]
+        self.splits = splits                                # > 0: decoded tokens' keys are cut into this many parts
         self.part = MIXERS.get(kind)(params, env(width, self.dt), "")
         names = {d.name for d in self.part.declare()}
         assert names == set(W), (sorted(names), sorted(W))
@@ -103,6 +104,7 @@ class Bench:
             entries.append(StepEntry(r, [0] * rows.shape[0], []))
             starts.append(start)
         _, _, ctx = self.pb.build(entries, starts)
+        ctx.decode_splits = self.splits
         out = self.part.forward(dev(torch.cat([rows for _, rows in portions]), self.dt), ctx, self.binding)
         for e, s in zip(entries, starts):
             self.m.advance(e.req_id, s + len(e.tokens))
@@ -267,7 +269,7 @@ def test_latent_attention_window_sink_gate(dtype, H_, D, Pr, V, R, Rq, window, r
              position=PartSpec("rope", {"head_dim": Pr, "rotary_dim": rot, "theta": 300.0, "max_positions": 1024, "style": "neox",
                                         "ramp": sc}))
     W = weights_for(MIXERS.get("latent_attention")(p, env(width, torch.float32), "").declare(), dtype, H_ + D, std=0.2,
-                    scale={"mix.sink": 15.0, "mix.uq": 3.0})
+                    scale={"mix.sink": 15.0, "mix.uq": 3.0 * (16.0 / (D + Pr)) ** 0.5})      # scores as sharp at every head size
     for k in ("mix.dq.norm", "mix.dkv.norm"):
         W[k] = (W[k] + 1.0).to(torch.bfloat16).float()
     bench = Bench("latent_attention", p, W, dtype, width, block_size=block_size, num_blocks=512 // block_size)
@@ -280,11 +282,12 @@ def test_latent_attention_window_sink_gate(dtype, H_, D, Pr, V, R, Rq, window, r
         close(got[r], want, dtype, r)
 
 
-DIFF = [(4, 2, 8, 16, 9, 3, 16), (6, 1, 24, 40, 7, 0, 16), (3, 3, 10, 6, 1, 5, 4), (9, 3, 6, 14, 40, 17, 8), (4, 2, 64, 128, 64, 4, 64),
-        (2, 2, 32, 32, 200, 70, 16)]
+# the last five have sizes that the tensor-core kernel takes in bfloat16 (maps of 32, 64, 128; values of 64, 128)
+DIFF = [(4, 2, 8, 16, 9, 3, 16), (6, 1, 24, 40, 7, 0, 16), (3, 3, 10, 6, 1, 5, 4), (9, 3, 6, 14, 40, 17, 8), (2, 2, 32, 32, 200, 70, 16),
+        (4, 2, 64, 128, 64, 4, 64), (4, 2, 32, 64, 40, 5, 16), (8, 1, 32, 64, 30, 70, 8), (2, 2, 128, 64, 50, 3, 32), (3, 1, 64, 64, 1, 2, 4)]
 
 
-def diff_case(dtype, H_, G, D, V, window, keep, block_size, inputs=None, tie=False, width=64, plan=PLAN, seed=0):
+def diff_case(dtype, H_, G, D, V, window, keep, block_size, inputs=None, tie=False, width=64, plan=PLAN, seed=0, splits=0):
     from dinfer_b200.parts.base import MIXERS
     import dinfer_b200.models.decoder  # noqa: F401
     names = dict(q_proj="mix.q", k_proj="mix.k", v_proj="mix.v", gate_proj="mix.g", o_proj="mix.o", lambda_q1="mix.lq1",
@@ -294,7 +297,7 @@ def diff_case(dtype, H_, G, D, V, window, keep, block_size, inputs=None, tie=Fal
                     scale={"lq1": 4.0, "lk1": 4.0, "lq2": 4.0, "lk2": 4.0})
     if tie:                                                  # a key made of a token answers the query made of the same token
         W["mix.k"] = W["mix.q"].view(G, H_ // G, 2 * D, width)[:, 0].reshape(G * 2 * D, width).clone()
-    bench = Bench("differential_attention", p, W, dtype, width, block_size=block_size, num_blocks=512 // block_size)
+    bench = Bench("differential_attention", p, W, dtype, width, block_size=block_size, num_blocks=1024 // block_size, splits=splits)
     inputs = inputs if inputs is not None else rows_for(width, dtype, 9)
     got = run_cut(bench, inputs, plan)
     m = {"heads": H_, "kv_heads": G, "dim": D, "vdim": V, "scale": 0.5, "diff": 0.35, "mask": {"size": window, "keep_first": keep}}
@@ -311,14 +314,31 @@ def test_differential_attention(dtype, H_, G, D, V, window, keep, block_size):
         close(got[r], want[r], dtype, r)
 
 
+@pytest.mark.parametrize("splits", [1, 3, 16])
+def test_differential_attention_decodes_with_split_keys(splits):
+    """Decoded tokens on the tensor cores with their keys cut into parts: kept first tokens on tiles of their own far
+    before the window, parts that get no tile at all, a short request beside a long one."""
+    g = torch.Generator().manual_seed(11)
+    rows = {"a": torch.randn(420, 64, generator=g).to(torch.bfloat16).float(), "b": torch.randn(9, 64, generator=g).to(torch.bfloat16).float()}
+    plan = [{"a": 400, "b": 3}] + [{"a": 1, "b": 1}] * 6 + [{"a": 14}]
+    got, want = diff_case("bfloat16", 4, 2, 32, 64, 150, 70, 16, inputs=rows, plan=plan, splits=splits)
+    for r in want:
+        close(got[r], want[r], "bfloat16", r)
+
+
+# sizes for the plain-arithmetic kernel (32-bit) and for the tensor-core kernel (bfloat16)
+EDGE_SIZES = {"float32": (4, 2, 16, 24), "bfloat16": (4, 2, 32, 64)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("new", [1, 6])
 @pytest.mark.parametrize("where", ["window_in", "window_out", "kept_in", "kept_out"])
-def test_differential_attention_keys_at_the_edges(new, where):
+def test_differential_attention_keys_at_the_edges(new, where, dtype):
     """One key made to dominate (its token's row is a multiple of the query token's and keys are tied to queries):
     just inside and just outside the window, the last kept first token and the one behind it, for the last token of
     a prompt portion and for a decoded one.  Outside it must leave no trace; pages of 4 put the kept tokens on
-    pages the window has long passed."""
-    window, keep, hist = 24, 6, 61
+    pages the window has long passed, and a history of 131 puts them on a tile of keys of their own."""
+    window, keep, hist = 24, 6, 131
     q_at = hist + new - 1
     k_at = {"window_in": q_at - window + 1, "window_out": q_at - window, "kept_in": keep - 1, "kept_out": keep}[where]
     g = torch.Generator().manual_seed(3)
@@ -327,9 +347,10 @@ def test_differential_attention_keys_at_the_edges(new, where):
     plain = {k: v.clone() for k, v in rows.items()}
     rows["a"][k_at] = rows["a"][q_at] * 3.0
     plan = [{"a": hist, "b": 31}, {"a": new, "b": 2}]
-    got, want = diff_case("float32", 4, 2, 16, 24, window, keep, 4, inputs=rows, tie=True, plan=plan)
-    close(got["a"], want["a"], "float32")
-    base, _ = diff_case("float32", 4, 2, 16, 24, window, keep, 4, inputs=plain, tie=True, plan=plan)
+    H_, G, D, V = EDGE_SIZES[dtype]
+    got, want = diff_case(dtype, H_, G, D, V, window, keep, 4, inputs=rows, tie=True, plan=plan)
+    close(got["a"], want["a"], dtype)
+    base, _ = diff_case(dtype, H_, G, D, V, window, keep, 4, inputs=plain, tie=True, plan=plan)
     moved = float((got["a"][q_at] - base["a"][q_at]).abs().max())
     assert (moved > 1e-2) == where.endswith("_in"), moved
 
