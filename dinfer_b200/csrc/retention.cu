@@ -13,6 +13,17 @@
 //                    one.  Prompt portions and decoded tokens run in the same launch.  The powers of d are made once
 //                    per CTA in 64-bit and rounded to 32-bit.
 //
+// retention_sums / retention_scan / retention_outputs
+//                    The same three lines for steps with long prompt portions, where a chain over the chunks would
+//                    leave most of the device idle.  Because d is a constant, the chunks' own sums
+//                        U_c = sum_s d^(n-1-s) k_s v_s^T
+//                    need no state: one launch makes them for every (request, head, chunk of 64 tokens) at once
+//                    (32-bit multiply-adds, 64 x 64 tiles of U, four by four outputs a thread).  A second launch
+//                    walks the chunks of a request per element of S, S <- d^n S + U_c, and leaves in U_c's place the
+//                    S that chunk c starts from; the last S goes back to the state row.  The third launch makes
+//                    every chunk's outputs from its q, k, v and that S, a (chunk, head, 64 value columns) per CTA.
+//                    The work space holds one [H, dk, dv] matrix per chunk.
+//
 // Everything here is 32-bit: q, k, v arrive as 32-bit rows (the projection's result is not rounded on its way in).
 #include "common.cuh"
 
@@ -142,6 +153,185 @@ retention_chunks_kernel(const float* __restrict__ q, const float* __restrict__ k
   }
 }
 
+// ------------------------------------------------------------------------------------------------ chunks side by side
+constexpr int CP = 64;           // tokens per chunk
+constexpr int TP = 64;           // tile edge: key channels x value columns (sums), tokens x value columns (outputs)
+constexpr int KT = 32;           // key channels per pass of the outputs kernel
+constexpr int LDT = TP + 4;      // row stride of the transposed tiles (rows stay 16-byte aligned)
+
+struct ChunkParams {
+  const float* q; const float* k; const float* v; int64_t ldq, ldk, ldv;
+  const float* decay; float* state; int64_t ld_state;
+  const int* cu_seqlens; const int* slots; const int* fresh;
+  float* out; float* work;       // work: [chunk slots][H][dk][dv]
+  int H, dk, dv; float k_scale;
+};
+
+// request b's chunk c lives in work slot t_begin / CP + b + c: slots of different requests never meet, and there are at
+// most T / CP + B of them
+__device__ __forceinline__ int64_t chunk_slot(int t_begin, int b, int c) { return (int64_t)(t_begin / CP + b + c); }
+
+// U_c for one (chunk, head, 64 x 64 tile of [dk, dv]); grid (chunks, H * tiles, B)
+__global__ void __launch_bounds__(THREADS) retention_sums_kernel(const ChunkParams p) {
+  __shared__ __align__(16) float k_s[CP][TP];      // [token][key channel]
+  __shared__ __align__(16) float w_s[CP][TP];      // [token][value column], scaled by d^(n-1-s)
+  __shared__ float pw[CP + 1];
+  pdl_enter();
+  const int tiles_v = (p.dv + TP - 1) / TP, tiles_k = (p.dk + TP - 1) / TP;
+  const int b = blockIdx.z, c = blockIdx.x;
+  const int h = blockIdx.y / (tiles_k * tiles_v), tile = blockIdx.y % (tiles_k * tiles_v);
+  const int e0 = (tile / tiles_v) * TP, c0 = (tile % tiles_v) * TP;
+  const int t_begin = p.cu_seqlens[b], t_end = p.cu_seqlens[b + 1];
+  const int t0 = t_begin + c * CP;
+  if (t0 >= t_end) return;
+  const int n = min(CP, t_end - t0), tid = threadIdx.x;
+  if (tid <= CP) pw[tid] = (float)pow((double)p.decay[h], (double)tid);
+  __syncthreads();
+  for (int i = tid; i < CP * TP; i += THREADS) {
+    const int s = i / TP, x = i % TP;
+    const bool live = s < n;
+    k_s[s][x] = (live && e0 + x < p.dk) ? p.k[(int64_t)(t0 + s) * p.ldk + (int64_t)h * p.dk + e0 + x] * p.k_scale : 0.f;
+    w_s[s][x] = (live && c0 + x < p.dv) ? p.v[(int64_t)(t0 + s) * p.ldv + (int64_t)h * p.dv + c0 + x] * pw[n - 1 - s] : 0.f;
+  }
+  __syncthreads();
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+  for (int s = 0; s < n; ++s) {
+    const float4 a = *reinterpret_cast<const float4*>(&k_s[s][ty * 4]);
+    const float4 w = *reinterpret_cast<const float4*>(&w_s[s][tx * 4]);
+    const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+  }
+  float* U = p.work + (chunk_slot(t_begin, b, c) * p.H + h) * (int64_t)p.dk * p.dv;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + ty * 4 + i, x = c0 + tx * 4 + j;
+      if (e < p.dk && x < p.dv) U[(int64_t)e * p.dv + x] = acc[i][j];
+    }
+}
+
+// per element of S: walk the request's chunks; grid (elements / THREADS, B)
+__global__ void __launch_bounds__(THREADS) retention_scan_kernel(const ChunkParams p) {
+  pdl_enter();
+  const int b = blockIdx.y;
+  const int64_t per_head = (int64_t)p.dk * p.dv, total = per_head * p.H;
+  const int64_t i = (int64_t)blockIdx.x * THREADS + threadIdx.x;
+  const int t_begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - t_begin;
+  if (i >= total || len <= 0) return;
+  const double d = (double)p.decay[i / per_head];
+  const float d_full = (float)pow(d, (double)CP);
+  float* S_g = p.state + (int64_t)p.slots[b] * p.ld_state + i;
+  float S = p.fresh[b] ? 0.f : *S_g;
+  float* U = p.work + chunk_slot(t_begin, b, 0) * total + i;
+  const int chunks = (len + CP - 1) / CP;
+  int c = 0;
+  for (; c + 4 <= chunks - 1; c += 4) {          // whole chunks, four loads in flight
+    float u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) u[j] = U[(int64_t)(c + j) * total];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { U[(int64_t)(c + j) * total] = S; S = fmaf(S, d_full, u[j]); }
+  }
+  for (; c < chunks; ++c) {
+    const int n = min(CP, len - c * CP);
+    const float u = U[(int64_t)c * total];
+    U[(int64_t)c * total] = S;
+    S = fmaf(S, n == CP ? d_full : (float)pow(d, (double)n), u);
+  }
+  *S_g = S;
+}
+
+// o for one (chunk, head, 64 value columns); grid (chunks, H * column tiles, B)
+__global__ void __launch_bounds__(THREADS) retention_outputs_kernel(const ChunkParams p) {
+  __shared__ __align__(16) float tiles[2 * KT * LDT + KT * TP];
+  static_assert(CP * LDT <= 2 * KT * LDT + KT * TP, "A takes the place of the passes' tiles");
+  float (*qT)[LDT] = reinterpret_cast<float (*)[LDT]>(tiles);                    // [key channel][token]
+  float (*kT)[LDT] = reinterpret_cast<float (*)[LDT]>(tiles + KT * LDT);         // [key channel][token]
+  float (*S_s)[TP] = reinterpret_cast<float (*)[TP]>(tiles + 2 * KT * LDT);      // [key channel][value column]
+  float (*AT)[LDT] = reinterpret_cast<float (*)[LDT]>(tiles);                    // [token s][token t], after the passes
+  __shared__ __align__(16) float v_s[CP][TP];      // [token s][value column]
+  __shared__ float pw[CP + 1];
+  pdl_enter();
+  const int tiles_v = (p.dv + TP - 1) / TP;
+  const int b = blockIdx.z, c = blockIdx.x, h = blockIdx.y / tiles_v, c0 = (blockIdx.y % tiles_v) * TP;
+  const int t_begin = p.cu_seqlens[b], t_end = p.cu_seqlens[b + 1];
+  const int t0 = t_begin + c * CP;
+  if (t0 >= t_end) return;
+  const int n = min(CP, t_end - t0), tid = threadIdx.x;
+  const int ty = tid >> 4, tx = tid & 15;
+  if (tid <= CP) pw[tid] = (float)pow((double)p.decay[h], (double)tid);
+  for (int i = tid; i < CP * TP; i += THREADS) {
+    const int s = i / TP, x = i % TP;
+    v_s[s][x] = (s < n && c0 + x < p.dv) ? p.v[(int64_t)(t0 + s) * p.ldv + (int64_t)h * p.dv + c0 + x] : 0.f;
+  }
+  const float* S_prev = p.work + (chunk_slot(t_begin, b, c) * p.H + h) * (int64_t)p.dk * p.dv;
+  float a[4][4] = {}, r[4][4] = {};
+  for (int e0 = 0; e0 < p.dk; e0 += KT) {
+    __syncthreads();                               // the last pass is done with the tiles (and pw, v_s are written)
+    for (int i = tid; i < CP * KT; i += THREADS) {
+      const int t = i / KT, e = i % KT;
+      const bool live = t < n && e0 + e < p.dk;
+      qT[e][t] = live ? p.q[(int64_t)(t0 + t) * p.ldq + (int64_t)h * p.dk + e0 + e] : 0.f;
+      kT[e][t] = live ? p.k[(int64_t)(t0 + t) * p.ldk + (int64_t)h * p.dk + e0 + e] * p.k_scale : 0.f;
+    }
+    for (int i = tid; i < KT * TP; i += THREADS) {
+      const int e = i / TP, x = i % TP;
+      S_s[e][x] = (e0 + e < p.dk && c0 + x < p.dv) ? S_prev[(int64_t)(e0 + e) * p.dv + c0 + x] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int e = 0; e < KT; ++e) {
+      const float4 q4 = *reinterpret_cast<const float4*>(&qT[e][ty * 4]);
+      const float4 k4 = *reinterpret_cast<const float4*>(&kT[e][tx * 4]);
+      const float4 s4 = *reinterpret_cast<const float4*>(&S_s[e][tx * 4]);
+      const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { a[i][j] = fmaf(qv[i], kv[j], a[i][j]); r[i][j] = fmaf(qv[i], sv[j], r[i][j]); }
+    }
+  }
+  __syncthreads();                                 // everyone is done with the tiles: A takes their place
+  // the decay between the two tokens, nothing for tokens ahead; A goes to shared memory with t along the rows' ends
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int s = tx * 4 + j;
+    float col[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = ty * 4 + i;
+      col[i] = (s <= t && t < n) ? a[i][j] * pw[t - s] : 0.f;
+    }
+    *reinterpret_cast<float4*>(&AT[s][ty * 4]) = make_float4(col[0], col[1], col[2], col[3]);
+  }
+  __syncthreads();
+  float o[4][4] = {};
+  const int last = min(ty * 4 + 3, n - 1);
+  for (int s = 0; s <= last; ++s) {
+    const float4 a4 = *reinterpret_cast<const float4*>(&AT[s][ty * 4]);
+    const float4 v4 = *reinterpret_cast<const float4*>(&v_s[s][tx * 4]);
+    const float av[4] = {a4.x, a4.y, a4.z, a4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[i][j] = fmaf(av[i], vv[j], o[i][j]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = ty * 4 + i;
+    if (t >= n) continue;
+    float* dst = p.out + (int64_t)(t0 + t) * p.H * p.dv + (int64_t)h * p.dv + c0 + tx * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (c0 + tx * 4 + j < p.dv) dst[j] = o[i][j] + pw[t + 1] * r[i][j];
+  }
+}
+
 }  // namespace
 
 DINFER_DEFINE_LAST_ERROR()
@@ -168,4 +358,30 @@ DINFER_API int dinfer_retention(const float* q, const float* k, const float* v, 
   launch_pdl(retention_chunks_kernel, dim3((dv + DVS - 1) / DVS, H, B), dim3(THREADS), smem, stream, q, k, v, ldq, ldk, ldv,
              decay, state, ld_state, cu_seqlens, slots, fresh, out, H, dk, dv, k_scale);
   return cuda_status("retention");
+}
+
+// Tokens of a chunk of the side-by-side form, and the floats of work space it needs for a step of T tokens in B requests.
+DINFER_API int dinfer_retention_chunk_tokens() { return CP; }
+DINFER_API int64_t dinfer_retention_work_floats(int64_t T, int B, int H, int dk, int dv) {
+  return (T / CP + B) * (int64_t)H * dk * dv;
+}
+
+// The same contract as dinfer_retention, for steps whose longest portion has max_q_len tokens: chunks of 64 tokens side
+// by side.  work: dinfer_retention_work_floats() floats.
+DINFER_API int dinfer_retention_chunks(const float* q, const float* k, const float* v, int64_t ldq, int64_t ldk, int64_t ldv,
+                                       const float* decay, float* state, int64_t ld_state, const int* cu_seqlens,
+                                       const int* slots, const int* fresh, float* out, float* work, int B, int H, int dk,
+                                       int dv, float k_scale, int max_q_len, cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || dk <= 0 || dv <= 0 || B > 65535 || max_q_len <= 0 || !work)
+    return refuse(DINFER_BAD_ARGUMENT, "retention_chunks: bad sizes B=%d H=%d dk=%d dv=%d longest=%d", B, H, dk, dv, max_q_len);
+  if (ldq < (int64_t)H * dk || ldk < (int64_t)H * dk || ldv < (int64_t)H * dv || ld_state < (int64_t)H * dk * dv)
+    return refuse(DINFER_BAD_ARGUMENT, "retention_chunks: a row stride is shorter than its row");
+  const int tiles_k = (dk + TP - 1) / TP, tiles_v = (dv + TP - 1) / TP, chunks = (max_q_len + CP - 1) / CP;
+  if ((int64_t)H * tiles_k * tiles_v > 65535) return refuse(DINFER_BAD_ARGUMENT, "retention_chunks: too many tiles for the grid");
+  ChunkParams p{q, k, v, ldq, ldk, ldv, decay, state, ld_state, cu_seqlens, slots, fresh, out, work, H, dk, dv, k_scale};
+  launch_pdl(retention_sums_kernel, dim3(chunks, H * tiles_k * tiles_v, B), dim3(THREADS), 0, stream, p);
+  const int64_t total = (int64_t)H * dk * dv;
+  launch_pdl(retention_scan_kernel, dim3((unsigned)((total + THREADS - 1) / THREADS), B), dim3(THREADS), 0, stream, p);
+  launch_pdl(retention_outputs_kernel, dim3(chunks, H * tiles_v, B), dim3(THREADS), 0, stream, p);
+  return cuda_status("retention_chunks");
 }

@@ -85,12 +85,19 @@ def short_conv_input(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor,
     return out
 
 
+# Steps whose longest portion has more tokens than this take their chunks side by side (three launches) instead of
+# one after the other inside a CTA.
+RETENTION_CHAIN_TOKENS = 128
+
+
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
               cu_seqlens: torch.Tensor, slots: torch.Tensor, fresh: torch.Tensor, num_heads: int, key_dim: int,
-              value_dim: int, k_scale: float) -> torch.Tensor:
+              value_dim: int, k_scale: float, max_q_len: int = 0, side_by_side: Optional[bool] = None) -> torch.Tensor:
     """``S_t = decay_h S_(t-1) + (k_scale k_t) v_t^T; o_t = S_t^T q_t`` per request and head, S [dk, dv] in the first
     ``H * dk * dv`` elements of row ``slots[b]`` of ``state`` (f32 rows, any row stride; zero for a fresh request).
-    q, k [T, H * dk], v [T, H * dv]: float32 rows (views with a row stride are fine).  Returns o f32 [T, H, dv]."""
+    q, k [T, H * dk], v [T, H * dv]: float32 rows (views with a row stride are fine).  Returns o f32 [T, H, dv].
+    ``max_q_len``: the longest portion of the step (0: not known); long portions run their chunks side by side, which
+    ``side_by_side`` forces or forbids."""
     require_cuda(q, k, v, decay, state, cu_seqlens, slots, fresh)
     _ints(cu_seqlens, slots, fresh)
     T = q.shape[0]
@@ -105,10 +112,26 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
     out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
     if T == 0:
         return out
+    B = cu_seqlens.numel() - 1
+    if side_by_side is None:
+        side_by_side = max_q_len > RETENTION_CHAIN_TOKENS
+    if side_by_side:
+        longest = int(max_q_len) if max_q_len > 0 else T
+        lib, f = _fn("retention", "dinfer_retention_chunks",
+                     [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+        chunk = 64                                        # tokens of a chunk in the kernels (CP)
+        work = torch.empty((T // chunk + B) * H * dk * dv, dtype=torch.float32, device=q.device)
+        check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(decay), ptr(state), state.stride(0),
+                     ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), ptr(work), B, H, dk, dv, float(k_scale), longest,
+                     stream_handle()), "retention_chunks")
+        from .lib import add_launches
+        add_launches(2)                                   # three launches in all
+        return out
     lib, f = _fn("retention", "dinfer_retention",
                  [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
     check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(decay), ptr(state), state.stride(0),
-                 ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), cu_seqlens.numel() - 1, H, dk, dv, float(k_scale),
+                 ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), B, H, dk, dv, float(k_scale),
                  stream_handle()), "retention")
     return out

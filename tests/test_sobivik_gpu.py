@@ -229,12 +229,46 @@ def test_retention_remembers_a_far_token():
     at, outs = 0, []
     for n in (1, 2, 40, 33, 1, 1, 200, 22, 1):
         o = stream_ops.retention(dev(q[at:at + n]), dev(k[at:at + n]), dev(v[at:at + n]), decay, state, i32([0, n]), i32([1]),
-                                 i32([1 if at == 0 else 0]), 1, dk, dv, 1.0)
+                                 i32([1 if at == 0 else 0]), 1, dk, dv, 1.0, max_q_len=n)
         outs.append(o.cpu())
         at += n
     got = torch.cat(outs)[T - 1, 0]
     assert torch.allclose(got, v[0] * 0.999 ** 300, atol=1e-6, rtol=1e-5)
     assert torch.isnan(state[1, dk * dv:]).all() and torch.isnan(state[0]).all()      # nothing beside its own row
+
+
+@pytest.mark.parametrize("H_, dk, dv", [(2, 16, 24), (3, 128, 40), (1, 12, 20), (2, 64, 64), (5, 33, 7), (1, 72, 130)])
+@pytest.mark.parametrize("side_by_side", [True, False])
+def test_retention_chunk_forms(H_, dk, dv, side_by_side):
+    """Both forms of the kernel (chunks one after the other, chunks side by side) against the recurrence token by
+    token in 64-bit: unequal requests in one step, portions that end on a chunk's edge, one token before and one
+    behind it, single tokens, a state that an earlier step left and rows that another request used."""
+    from dinfer_b200.kernels import stream_ops
+    g = torch.Generator().manual_seed(dk * 7 + dv)
+    decay = torch.tensor([1.0 - 0.2 ** (i + 1) for i in range(H_)], dtype=F64)
+    plans = [[(0, 130), (2, 1), (1, 64)], [(0, 63), (1, 65), (2, 1), (3, 2)], [(3, 128), (0, 1), (1, 192), (2, 7)]]
+    state = torch.full((5, H_ * dk * dv + 3), float("nan"), device="cuda")
+    S = {r: torch.zeros(H_, dk, dv, dtype=F64) for r in range(4)}
+    seen = set()
+    for plan in plans:
+        T = sum(n for _, n in plan)
+        q, k, v = (torch.randn(T, H_, d, generator=g) for d in (dk, dk, dv))
+        cu = [0]
+        for _, n in plan:
+            cu.append(cu[-1] + n)
+        fresh = [0 if r in seen else 1 for r, _ in plan]
+        o = stream_ops.retention(dev(q.reshape(T, -1)), dev(k.reshape(T, -1)), dev(v.reshape(T, -1)), dev(decay.float()), state,
+                                 i32(cu), i32([r + 1 for r, _ in plan]), i32(fresh), H_, dk, dv, 0.5,
+                                 max_q_len=max(n for _, n in plan), side_by_side=side_by_side).cpu().double()
+        for i, (r, n) in enumerate(plan):
+            seen.add(r)
+            for t in range(cu[i], cu[i + 1]):
+                S[r] = decay[:, None, None] * S[r] + 0.5 * k[t].double()[:, :, None] * v[t].double()[:, None, :]
+                want = torch.einsum("hkv,hk->hv", S[r], q[t].double())
+                assert torch.allclose(o[t], want, atol=2e-4, rtol=2e-4), (plan, r, t - cu[i])
+    for r in range(4):
+        assert torch.allclose(state[r + 1, :H_ * dk * dv].cpu().double().view(H_, dk, dv), S[r], atol=2e-4, rtol=2e-4)
+    assert torch.isnan(state[0]).all() and torch.isnan(state[:, H_ * dk * dv:]).all()
 
 
 def test_ramp_rotation_table():
