@@ -10,8 +10,9 @@
 //                    which is the recurrence written out; only the order of the sums differs.  One CTA owns one
 //                    (request, head, slice of 32 value columns): its slice of S stays in shared memory over all chunks
 //                    of the step and goes back to the request's state row at the end.  A decoded token is a chunk of
-//                    one.  Prompt portions and decoded tokens run in the same launch.  The powers of d are made once
-//                    per CTA in 64-bit and rounded to 32-bit.
+//                    one.  Prompt portions and decoded tokens run in the same launch.  The powers d^0 .. d^64 come as
+//                    a table per head, made once in 64-bit and rounded to 32-bit (64-bit pow() in every CTA cost
+//                    more than the sums themselves).
 //
 // retention_sums / retention_scan / retention_outputs
 //                    The same three lines for steps with long prompt portions, where a chain over the chunks would
@@ -34,10 +35,11 @@ namespace {
 constexpr int C = 32;            // tokens per chunk
 constexpr int DVS = 32;          // value columns per CTA
 constexpr int THREADS = 256;
+constexpr int POWERS = 65;       // entries of a head's table of powers: d^0 .. d^64
 
 __global__ void __launch_bounds__(THREADS)
 retention_chunks_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                        int64_t ldq, int64_t ldk, int64_t ldv, const float* __restrict__ decay,
+                        int64_t ldq, int64_t ldk, int64_t ldv, const float* __restrict__ powers,
                         float* __restrict__ state, int64_t ld_state, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ slots, const int* __restrict__ fresh, float* __restrict__ out,
                         int H, int dk, int dv, float k_scale) {
@@ -62,7 +64,7 @@ retention_chunks_kernel(const float* __restrict__ q, const float* __restrict__ k
     const int kk = i / DVS, c = i % DVS;
     S_s[i] = (!is_fresh && c < cols) ? S_g[(int64_t)kk * dv + c] : 0.f;
   }
-  if (tid <= C) pw[tid] = (float)pow((double)decay[h], (double)tid);
+  if (tid <= C) pw[tid] = powers[h * POWERS + tid];
   __syncthreads();
 
   for (int t0 = t_begin; t0 < t_end; t0 += C) {
@@ -161,7 +163,7 @@ constexpr int LDT = TP + 4;      // row stride of the transposed tiles (rows sta
 
 struct ChunkParams {
   const float* q; const float* k; const float* v; int64_t ldq, ldk, ldv;
-  const float* decay; float* state; int64_t ld_state;
+  const float* powers; float* state; int64_t ld_state;
   const int* cu_seqlens; const int* slots; const int* fresh;
   float* out; float* work;       // work: [chunk slots][H][dk][dv]
   int H, dk, dv; float k_scale;
@@ -185,7 +187,7 @@ __global__ void __launch_bounds__(THREADS) retention_sums_kernel(const ChunkPara
   const int t0 = t_begin + c * CP;
   if (t0 >= t_end) return;
   const int n = min(CP, t_end - t0), tid = threadIdx.x;
-  if (tid <= CP) pw[tid] = (float)pow((double)p.decay[h], (double)tid);
+  if (tid <= CP) pw[tid] = p.powers[h * POWERS + tid];
   __syncthreads();
   for (int i = tid; i < CP * TP; i += THREADS) {
     const int s = i / TP, x = i % TP;
@@ -223,8 +225,8 @@ __global__ void __launch_bounds__(THREADS) retention_scan_kernel(const ChunkPara
   const int64_t i = (int64_t)blockIdx.x * THREADS + threadIdx.x;
   const int t_begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - t_begin;
   if (i >= total || len <= 0) return;
-  const double d = (double)p.decay[i / per_head];
-  const float d_full = (float)pow(d, (double)CP);
+  const float* pw = p.powers + (i / per_head) * POWERS;
+  const float d_full = pw[CP];
   float* S_g = p.state + (int64_t)p.slots[b] * p.ld_state + i;
   float S = p.fresh[b] ? 0.f : *S_g;
   float* U = p.work + chunk_slot(t_begin, b, 0) * total + i;
@@ -241,7 +243,7 @@ __global__ void __launch_bounds__(THREADS) retention_scan_kernel(const ChunkPara
     const int n = min(CP, len - c * CP);
     const float u = U[(int64_t)c * total];
     U[(int64_t)c * total] = S;
-    S = fmaf(S, n == CP ? d_full : (float)pow(d, (double)n), u);
+    S = fmaf(S, pw[n], u);
   }
   *S_g = S;
 }
@@ -249,6 +251,7 @@ __global__ void __launch_bounds__(THREADS) retention_scan_kernel(const ChunkPara
 // o for one (chunk, head, 64 value columns); grid (chunks, H * column tiles, B)
 __global__ void __launch_bounds__(THREADS) retention_outputs_kernel(const ChunkParams p) {
   __shared__ __align__(16) float tiles[2 * KT * LDT + KT * TP];
+  static_assert(CP + 1 == POWERS && C < POWERS, "the table covers a chunk");
   static_assert(CP * LDT <= 2 * KT * LDT + KT * TP, "A takes the place of the passes' tiles");
   float (*qT)[LDT] = reinterpret_cast<float (*)[LDT]>(tiles);                    // [key channel][token]
   float (*kT)[LDT] = reinterpret_cast<float (*)[LDT]>(tiles + KT * LDT);         // [key channel][token]
@@ -264,7 +267,7 @@ __global__ void __launch_bounds__(THREADS) retention_outputs_kernel(const ChunkP
   if (t0 >= t_end) return;
   const int n = min(CP, t_end - t0), tid = threadIdx.x;
   const int ty = tid >> 4, tx = tid & 15;
-  if (tid <= CP) pw[tid] = (float)pow((double)p.decay[h], (double)tid);
+  if (tid <= CP) pw[tid] = p.powers[h * POWERS + tid];
   for (int i = tid; i < CP * TP; i += THREADS) {
     const int s = i / TP, x = i % TP;
     v_s[s][x] = (s < n && c0 + x < p.dv) ? p.v[(int64_t)(t0 + s) * p.ldv + (int64_t)h * p.dv + c0 + x] : 0.f;
@@ -336,11 +339,11 @@ __global__ void __launch_bounds__(THREADS) retention_outputs_kernel(const ChunkP
 
 DINFER_DEFINE_LAST_ERROR()
 
-// q, k [T, >= H * dk] and v [T, >= H * dv]: f32 rows of strides ldq, ldk, ldv (head h at h * dk / h * dv); decay [H] f32;
+// q, k [T, >= H * dk] and v [T, >= H * dv]: f32 rows of strides ldq, ldk, ldv (head h at h * dk / h * dv); powers [H, 65] f32, row h = d_h^0 .. d_h^64;
 // state: f32 rows of stride ld_state, the first H * dk * dv elements of row slots[b] are request b's S; cu_seqlens [B + 1],
 // slots [B], fresh [B] (1: the request starts, S is zero whatever the row holds); out [T, H, dv] f32 contiguous.
 DINFER_API int dinfer_retention(const float* q, const float* k, const float* v, int64_t ldq, int64_t ldk, int64_t ldv,
-                                const float* decay, float* state, int64_t ld_state, const int* cu_seqlens,
+                                const float* powers, float* state, int64_t ld_state, const int* cu_seqlens,
                                 const int* slots, const int* fresh, float* out, int B, int H, int dk, int dv,
                                 float k_scale, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
@@ -356,12 +359,13 @@ DINFER_API int dinfer_retention(const float* q, const float* k, const float* v, 
     opted = 200 * 1024;
   }
   launch_pdl(retention_chunks_kernel, dim3((dv + DVS - 1) / DVS, H, B), dim3(THREADS), smem, stream, q, k, v, ldq, ldk, ldv,
-             decay, state, ld_state, cu_seqlens, slots, fresh, out, H, dk, dv, k_scale);
+             powers, state, ld_state, cu_seqlens, slots, fresh, out, H, dk, dv, k_scale);
   return cuda_status("retention");
 }
 
 // Tokens of a chunk of the side-by-side form, and the floats of work space it needs for a step of T tokens in B requests.
 DINFER_API int dinfer_retention_chunk_tokens() { return CP; }
+DINFER_API int dinfer_retention_powers() { return POWERS; }
 DINFER_API int64_t dinfer_retention_work_floats(int64_t T, int B, int H, int dk, int dv) {
   return (T / CP + B) * (int64_t)H * dk * dv;
 }
@@ -369,7 +373,7 @@ DINFER_API int64_t dinfer_retention_work_floats(int64_t T, int B, int H, int dk,
 // The same contract as dinfer_retention, for steps whose longest portion has max_q_len tokens: chunks of 64 tokens side
 // by side.  work: dinfer_retention_work_floats() floats.
 DINFER_API int dinfer_retention_chunks(const float* q, const float* k, const float* v, int64_t ldq, int64_t ldk, int64_t ldv,
-                                       const float* decay, float* state, int64_t ld_state, const int* cu_seqlens,
+                                       const float* powers, float* state, int64_t ld_state, const int* cu_seqlens,
                                        const int* slots, const int* fresh, float* out, float* work, int B, int H, int dk,
                                        int dv, float k_scale, int max_q_len, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || dk <= 0 || dv <= 0 || B > 65535 || max_q_len <= 0 || !work)
@@ -378,7 +382,7 @@ DINFER_API int dinfer_retention_chunks(const float* q, const float* k, const flo
     return refuse(DINFER_BAD_ARGUMENT, "retention_chunks: a row stride is shorter than its row");
   const int tiles_k = (dk + TP - 1) / TP, tiles_v = (dv + TP - 1) / TP, chunks = (max_q_len + CP - 1) / CP;
   if ((int64_t)H * tiles_k * tiles_v > 65535) return refuse(DINFER_BAD_ARGUMENT, "retention_chunks: too many tiles for the grid");
-  ChunkParams p{q, k, v, ldq, ldk, ldv, decay, state, ld_state, cu_seqlens, slots, fresh, out, work, H, dk, dv, k_scale};
+  ChunkParams p{q, k, v, ldq, ldk, ldv, powers, state, ld_state, cu_seqlens, slots, fresh, out, work, H, dk, dv, k_scale};
   launch_pdl(retention_sums_kernel, dim3(chunks, H * tiles_k * tiles_v, B), dim3(THREADS), 0, stream, p);
   const int64_t total = (int64_t)H * dk * dv;
   launch_pdl(retention_scan_kernel, dim3((unsigned)((total + THREADS - 1) / THREADS), B), dim3(THREADS), 0, stream, p);

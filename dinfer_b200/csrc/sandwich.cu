@@ -7,6 +7,8 @@
 //                      next  = z / sqrt(mean(z^2) + eps) * g_next, z = y or x_new, rounded    -> next_out  (optional)
 //                    `results` is one buffer of rows [count, T, h]: result j of token t at (j * T + t) * h.
 //                    One CTA per row, the row in shared memory; the norm that follows reads the row it has just made.
+//                    Rows whose length and strides are multiples of four go four elements a thread (16-byte loads,
+//                    up to 1024 threads a row), so that a decode step's few rows are not a chain of scalar loads.
 #include "common.cuh"
 
 using namespace dinfer;
@@ -49,6 +51,74 @@ gain_norm_join_kernel(const TA* __restrict__ a, int64_t lda, float g_a, const fl
   for (int i = threadIdx.x; i < h; i += blockDim.x) no[i] = from_f32<TO>(row[i] * fn);
 }
 
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  uint2 u;
+  *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TA, typename TO, typename TW>
+__global__ void __launch_bounds__(1024)
+gain_norm_join_vec_kernel(const TA* __restrict__ a, int64_t lda, float g_a, const float* __restrict__ x_in,
+                          float* __restrict__ x_out, float eps, const float* __restrict__ first,
+                          const float* __restrict__ results, int64_t result_stride, int n_results,
+                          const TW* __restrict__ w, float* __restrict__ avg_out, float g_next, TO* __restrict__ next_out,
+                          int h) {
+  extern __shared__ __align__(16) float row[];            // [h]
+  __shared__ float red[33];
+  pdl_enter();
+  const int64_t t = blockIdx.x;
+  const TA* ar = a + t * lda;
+  const int step = blockDim.x * 4;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < h; i += step) {
+    const float4 v = load4<TA>(ar + i);
+    *reinterpret_cast<float4*>(row + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  const float f = rsqrtf(block_sum(ss, red) / (float)h + eps) * g_a;
+  const float* xr = x_in + t * h;
+  float* xo = x_out + t * h;
+  const float w_first = avg_out ? to_f32<TW>(w[0]) : 0.f, w_last = avg_out ? to_f32<TW>(w[n_results]) : 0.f;
+  ss = 0.f;
+  for (int i = threadIdx.x * 4; i < h; i += step) {
+    const float4 x = load4<float>(xr + i), r = *reinterpret_cast<const float4*>(row + i);
+    float4 v = make_float4(x.x + r.x * f, x.y + r.y * f, x.z + r.z * f, x.w + r.w * f);
+    store4<float>(xo + i, v);
+    if (avg_out) {
+      const float4 p = load4<float>(first + t * h + i);
+      float4 y = make_float4(w_first * p.x, w_first * p.y, w_first * p.z, w_first * p.w);
+      for (int j = 1; j < n_results; ++j) {
+        const float wj = to_f32<TW>(w[j]);
+        const float4 q = load4<float>(results + (int64_t)(j - 1) * result_stride + t * h + i);
+        y.x = fmaf(wj, q.x, y.x); y.y = fmaf(wj, q.y, y.y); y.z = fmaf(wj, q.z, y.z); y.w = fmaf(wj, q.w, y.w);
+      }
+      v = make_float4(fmaf(w_last, v.x, y.x), fmaf(w_last, v.y, y.y), fmaf(w_last, v.z, y.z), fmaf(w_last, v.w, y.w));
+      store4<float>(avg_out + t * h + i, v);
+    }
+    *reinterpret_cast<float4*>(row + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (!next_out) return;
+  const float fn = rsqrtf(block_sum(ss, red) / (float)h + eps) * g_next;
+  TO* no = next_out + t * h;
+  for (int i = threadIdx.x * 4; i < h; i += step) {
+    const float4 r = *reinterpret_cast<const float4*>(row + i);
+    store4<TO>(no + i, make_float4(r.x * fn, r.y * fn, r.z * fn, r.w * fn));
+  }
+}
+
 }  // namespace
 
 DINFER_DEFINE_LAST_ERROR()
@@ -69,12 +139,16 @@ DINFER_API int dinfer_gain_norm_join(const void* a, int64_t lda, float g_a, cons
   DINFER_DISPATCH_DTYPE(a_dtype, TA,
     DINFER_DISPATCH_DTYPE(out_dtype, TO,
       DINFER_DISPATCH_DTYPE(w_dtype, TW, {
-        auto k = gain_norm_join_kernel<TA, TO, TW>;
+        const bool vec = h % 4 == 0 && lda % 4 == 0 && result_stride % 4 == 0 && (uintptr_t)a % 16 == 0 &&
+                         (uintptr_t)x_in % 16 == 0 && (uintptr_t)x_out % 16 == 0 && (uintptr_t)first % 16 == 0 &&
+                         (uintptr_t)results % 16 == 0 && (uintptr_t)avg_out % 16 == 0 && (uintptr_t)next_out % 16 == 0;
+        auto k = vec ? gain_norm_join_vec_kernel<TA, TO, TW> : gain_norm_join_kernel<TA, TO, TW>;
+        const int threads = vec ? min(1024, ((h / 4 + 31) / 32) * 32) : 256;
         if (smem > 48 * 1024) {
           cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
           if (e != cudaSuccess) return refuse((int)e, "gain_norm_join: shared memory opt-in failed: %s", cudaGetErrorString(e));
         }
-        launch_pdl(k, dim3(T), dim3(256), smem, stream, (const TA*)a, lda, g_a, x_in, x_out, eps, first, results,
+        launch_pdl(k, dim3(T), dim3(threads), smem, stream, (const TA*)a, lda, g_a, x_in, x_out, eps, first, results,
                    result_stride, n_results, (const TW*)w, avg_out, g_next, (TO*)next_out, h);
         return cuda_status("gain_norm_join");
       })));

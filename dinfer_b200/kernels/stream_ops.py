@@ -90,14 +90,24 @@ def short_conv_input(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor,
 RETENTION_CHAIN_TOKENS = 128
 
 
+RETENTION_POWERS = 65          # entries of a head's row of the table of powers (POWERS in the kernels)
+
+
+def retention_powers(decay: torch.Tensor) -> torch.Tensor:
+    """f32 [H, 65]: row h holds ``decay[h] ** 0 .. decay[h] ** 64``, made in 64-bit and rounded once."""
+    d = decay.detach().to(torch.float64).reshape(-1, 1)
+    return torch.pow(d, torch.arange(RETENTION_POWERS, dtype=torch.float64, device=decay.device)).to(torch.float32).contiguous()
+
+
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
               cu_seqlens: torch.Tensor, slots: torch.Tensor, fresh: torch.Tensor, num_heads: int, key_dim: int,
-              value_dim: int, k_scale: float, max_q_len: int = 0, side_by_side: Optional[bool] = None) -> torch.Tensor:
+              value_dim: int, k_scale: float, max_q_len: int = 0, side_by_side: Optional[bool] = None,
+              powers: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``S_t = decay_h S_(t-1) + (k_scale k_t) v_t^T; o_t = S_t^T q_t`` per request and head, S [dk, dv] in the first
     ``H * dk * dv`` elements of row ``slots[b]`` of ``state`` (f32 rows, any row stride; zero for a fresh request).
     q, k [T, H * dk], v [T, H * dv]: float32 rows (views with a row stride are fine).  Returns o f32 [T, H, dv].
     ``max_q_len``: the longest portion of the step (0: not known); long portions run their chunks side by side, which
-    ``side_by_side`` forces or forbids."""
+    ``side_by_side`` forces or forbids.  ``powers``: ``retention_powers(decay)``, for a caller that keeps it."""
     require_cuda(q, k, v, decay, state, cu_seqlens, slots, fresh)
     _ints(cu_seqlens, slots, fresh)
     T = q.shape[0]
@@ -112,6 +122,11 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
     out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
     if T == 0:
         return out
+    if powers is None:
+        powers = retention_powers(decay)
+    if powers.dtype != torch.float32 or tuple(powers.shape) != (H, RETENTION_POWERS) or not powers.is_contiguous():
+        raise KernelError("retention: powers float32 [H, 65]")
+    require_cuda(powers)
     B = cu_seqlens.numel() - 1
     if side_by_side is None:
         side_by_side = max_q_len > RETENTION_CHAIN_TOKENS
@@ -122,7 +137,7 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
         chunk = 64                                        # tokens of a chunk in the kernels (CP)
         work = torch.empty((T // chunk + B) * H * dk * dv, dtype=torch.float32, device=q.device)
-        check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(decay), ptr(state), state.stride(0),
+        check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(powers), ptr(state), state.stride(0),
                      ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), ptr(work), B, H, dk, dv, float(k_scale), longest,
                      stream_handle()), "retention_chunks")
         from .lib import add_launches
@@ -131,7 +146,7 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
     lib, f = _fn("retention", "dinfer_retention",
                  [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
-    check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(decay), ptr(state), state.stride(0),
+    check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(powers), ptr(state), state.stride(0),
                  ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), B, H, dk, dv, float(k_scale),
                  stream_handle()), "retention")
     return out

@@ -64,6 +64,7 @@ class Retention(Mixer):
         self.o = Linear(tensors[N["o"]])
         dev = rows[0].device
         self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=dev)
+        self.powers = stream_ops.retention_powers(self.decay)
         self.ones = torch.ones(self.dv, dtype=torch.float32, device=dev)
 
     def cache_need(self):
@@ -79,7 +80,7 @@ class Retention(Mixer):
         B = ctx.cu_seqlens.numel() - 1
         o = stream_ops.retention(P[:, :nq], P[:, nq:2 * nq], P[:, 2 * nq:2 * nq + nv], self.decay, cache.state,
                                  ctx.cu_seqlens, ctx.state_slots[:B], ctx.state_fresh[:B], self.H, self.dk, self.dv,
-                                 float(self.dk) ** -0.5, max_q_len=ctx.max_q_len)
+                                 float(self.dk) ** -0.5, max_q_len=ctx.max_q_len, powers=self.powers)
         y = torch.empty((T, nv), dtype=x.dtype, device=x.device)
         # the delta rule's output kernel does o / rms(o) * w * silu(gate); here w is all ones
         delta_ops.post(o, self.ones, P[:, 2 * nq + nv:], self.eps, False, y)

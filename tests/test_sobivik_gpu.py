@@ -35,7 +35,7 @@ def env(h, dt, maxpos=1024):
 # ---------------------------------------------------------------- the join of a sublayer to the stream
 
 @pytest.mark.parametrize("a_dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("h, n", [(72, 1), (256, 3), (1000, 6)])
+@pytest.mark.parametrize("h, n", [(72, 1), (70, 2), (256, 3), (1000, 6), (4100, 2)])
 def test_gain_norm_join(a_dtype, h, n):
     """Output norm, add, the average over n earlier results and the next input norm in one kernel; without the
     average; without the next norm; in place and out of place."""
