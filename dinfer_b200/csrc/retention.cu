@@ -42,7 +42,7 @@ retention_chunks_kernel(const float* __restrict__ q, const float* __restrict__ k
                         int64_t ldq, int64_t ldk, int64_t ldv, const float* __restrict__ powers,
                         float* __restrict__ state, int64_t ld_state, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ slots, const int* __restrict__ fresh, float* __restrict__ out,
-                        int H, int dk, int dv, float k_scale) {
+                        int H, int dk, int dv, float k_scale, int single_tokens) {
   extern __shared__ float smem[];
   const int dkp = dk + 1;
   float* q_s = smem;                       // [C][dk + 1]
@@ -60,6 +60,46 @@ retention_chunks_kernel(const float* __restrict__ q, const float* __restrict__ k
   const int cols = min(DVS, dv - c0);
   float* S_g = state + (int64_t)slots[b] * ld_state + ((int64_t)h * dk) * dv + c0;
   const bool is_fresh = fresh[b] != 0;
+  if (t_end - t_begin == 1) {
+    // ---- one token: S <- d S + k v^T and o = S^T q straight from and to the state row, a lane per value column and
+    // a warp per eighth of the key channels; the warps' shares of o meet in shared memory
+    const int c = tid & 31, w = tid >> 5;
+    const float d = powers[h * POWERS + 1];
+    const float* qr = q + (int64_t)t_begin * ldq + (int64_t)h * dk;
+    const float* kr = k + (int64_t)t_begin * ldk + (int64_t)h * dk;
+    const float vx = c < cols ? v[(int64_t)t_begin * ldv + (int64_t)h * dv + c0 + c] : 0.f;
+    float acc = 0.f;
+    if (c < cols) {
+      int kk = w;
+      for (; kk + 3 * (THREADS / 32) < dk; kk += 4 * (THREADS / 32)) {            // four rows of S in flight a lane
+        float sv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sv[u] = is_fresh ? 0.f : S_g[(int64_t)(kk + u * (THREADS / 32)) * dv + c];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int e = kk + u * (THREADS / 32);
+          const float x = fmaf(sv[u], d, kr[e] * k_scale * vx);
+          S_g[(int64_t)e * dv + c] = x;
+          acc = fmaf(x, qr[e], acc);
+        }
+      }
+      for (; kk < dk; kk += THREADS / 32) {
+        const float x = fmaf(is_fresh ? 0.f : S_g[(int64_t)kk * dv + c], d, kr[kk] * k_scale * vx);
+        S_g[(int64_t)kk * dv + c] = x;
+        acc = fmaf(x, qr[kk], acc);
+      }
+    }
+    smem[w * DVS + c] = acc;
+    __syncthreads();
+    if (w == 0 && c < cols) {
+      float o = 0.f;
+#pragma unroll
+      for (int u = 0; u < THREADS / 32; ++u) o += smem[u * DVS + c];
+      out[(int64_t)t_begin * H * dv + (int64_t)h * dv + c0 + c] = o;
+    }
+    return;
+  }
+  if (single_tokens) return;                 // the launch has no shared memory for chunks (its caller broke its word)
   for (int i = tid; i < dk * DVS; i += THREADS) {
     const int kk = i / DVS, c = i % DVS;
     S_s[i] = (!is_fresh && c < cols) ? S_g[(int64_t)kk * dv + c] : 0.f;
@@ -217,39 +257,56 @@ __global__ void __launch_bounds__(THREADS) retention_sums_kernel(const ChunkPara
     }
 }
 
-// per element of S: walk the request's chunks; grid (elements / THREADS, B)
+// per four neighbouring elements of S: walk the request's chunks; grid (elements / 4 / THREADS, B).  The walk is a chain
+// of loads that wait on nothing but memory, so a thread keeps eight chunks' loads of 16 bytes in flight and loads the
+// next eight before it stores the last ones.  V = 1 (one element a thread) is for value sizes that are no multiple of 4.
+template <int V>
 __global__ void __launch_bounds__(THREADS) retention_scan_kernel(const ChunkParams p) {
+  constexpr int DEPTH = 8;
+  struct alignas(4 * V) Vec { float x[V]; };
   pdl_enter();
   const int b = blockIdx.y;
   const int64_t per_head = (int64_t)p.dk * p.dv, total = per_head * p.H;
-  const int64_t i = (int64_t)blockIdx.x * THREADS + threadIdx.x;
+  const int64_t i = ((int64_t)blockIdx.x * THREADS + threadIdx.x) * V;
   const int t_begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - t_begin;
   if (i >= total || len <= 0) return;
   const float* pw = p.powers + (i / per_head) * POWERS;
   const float d_full = pw[CP];
   float* S_g = p.state + (int64_t)p.slots[b] * p.ld_state + i;
-  float S = p.fresh[b] ? 0.f : *S_g;
+  Vec S;
+  if (p.fresh[b]) {
+#pragma unroll
+    for (int e = 0; e < V; ++e) S.x[e] = 0.f;
+  } else {
+    S = *reinterpret_cast<const Vec*>(S_g);
+  }
   float* U = p.work + chunk_slot(t_begin, b, 0) * total + i;
-  const int chunks = (len + CP - 1) / CP;
-  int c = 0;
-  for (; c + 4 <= chunks - 1; c += 4) {          // whole chunks, four loads in flight
-    float u[4];
+  const int chunks = (len + CP - 1) / CP, last_n = len - (chunks - 1) * CP;
+  Vec u[DEPTH], nxt[DEPTH];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) u[j] = U[(int64_t)(c + j) * total];
+  for (int j = 0; j < DEPTH; ++j)
+    if (j < chunks) u[j] = *reinterpret_cast<const Vec*>(U + (int64_t)j * total);
+  for (int c = 0; c < chunks; c += DEPTH) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { U[(int64_t)(c + j) * total] = S; S = fmaf(S, d_full, u[j]); }
+    for (int j = 0; j < DEPTH; ++j)
+      if (c + DEPTH + j < chunks) nxt[j] = *reinterpret_cast<const Vec*>(U + (int64_t)(c + DEPTH + j) * total);
+#pragma unroll
+    for (int j = 0; j < DEPTH; ++j) {
+      if (c + j < chunks) {
+        *reinterpret_cast<Vec*>(U + (int64_t)(c + j) * total) = S;
+        const float dn = c + j == chunks - 1 ? pw[last_n] : d_full;
+#pragma unroll
+        for (int e = 0; e < V; ++e) S.x[e] = fmaf(S.x[e], dn, u[j].x[e]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < DEPTH; ++j) u[j] = nxt[j];
   }
-  for (; c < chunks; ++c) {
-    const int n = min(CP, len - c * CP);
-    const float u = U[(int64_t)c * total];
-    U[(int64_t)c * total] = S;
-    S = fmaf(S, pw[n], u);
-  }
-  *S_g = S;
+  *reinterpret_cast<Vec*>(S_g) = S;
 }
 
 // o for one (chunk, head, 64 value columns); grid (chunks, H * column tiles, B)
-__global__ void __launch_bounds__(THREADS) retention_outputs_kernel(const ChunkParams p) {
+__global__ void __launch_bounds__(THREADS, 4) retention_outputs_kernel(const ChunkParams p) {
   __shared__ __align__(16) float tiles[2 * KT * LDT + KT * TP];
   static_assert(CP + 1 == POWERS && C < POWERS, "the table covers a chunk");
   static_assert(CP * LDT <= 2 * KT * LDT + KT * TP, "A takes the place of the passes' tiles");
@@ -342,15 +399,18 @@ DINFER_DEFINE_LAST_ERROR()
 // q, k [T, >= H * dk] and v [T, >= H * dv]: f32 rows of strides ldq, ldk, ldv (head h at h * dk / h * dv); powers [H, 65] f32, row h = d_h^0 .. d_h^64;
 // state: f32 rows of stride ld_state, the first H * dk * dv elements of row slots[b] are request b's S; cu_seqlens [B + 1],
 // slots [B], fresh [B] (1: the request starts, S is zero whatever the row holds); out [T, H, dv] f32 contiguous.
+// single_tokens != 0: the caller knows that every request brings one token (T == B), and the launch asks for no more
+// shared memory than that path needs.
 DINFER_API int dinfer_retention(const float* q, const float* k, const float* v, int64_t ldq, int64_t ldk, int64_t ldv,
                                 const float* powers, float* state, int64_t ld_state, const int* cu_seqlens,
                                 const int* slots, const int* fresh, float* out, int B, int H, int dk, int dv,
-                                float k_scale, cudaStream_t stream) {
+                                float k_scale, int single_tokens, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
     return refuse(DINFER_BAD_ARGUMENT, "retention: bad sizes B=%d H=%d dk=%d dv=%d", B, H, dk, dv);
   if (ldq < (int64_t)H * dk || ldk < (int64_t)H * dk || ldv < (int64_t)H * dv || ld_state < (int64_t)H * dk * dv)
     return refuse(DINFER_BAD_ARGUMENT, "retention: a row stride is shorter than its row");
-  const size_t smem = sizeof(float) * ((size_t)2 * C * (dk + 1) + (size_t)dk * DVS + 2 * C * DVS + C * (C + 1) + C + 1);
+  const size_t smem = single_tokens ? sizeof(float) * (THREADS / 32) * DVS
+                                    : sizeof(float) * ((size_t)2 * C * (dk + 1) + (size_t)dk * DVS + 2 * C * DVS + C * (C + 1) + C + 1);
   if (smem > 200 * 1024) return refuse(DINFER_BAD_ARGUMENT, "retention: a key of %d channels needs %zu bytes of shared memory", dk, smem);
   static size_t opted = 0;
   if (smem > 48 * 1024 && smem > opted) {
@@ -359,7 +419,7 @@ DINFER_API int dinfer_retention(const float* q, const float* k, const float* v, 
     opted = 200 * 1024;
   }
   launch_pdl(retention_chunks_kernel, dim3((dv + DVS - 1) / DVS, H, B), dim3(THREADS), smem, stream, q, k, v, ldq, ldk, ldv,
-             powers, state, ld_state, cu_seqlens, slots, fresh, out, H, dk, dv, k_scale);
+             powers, state, ld_state, cu_seqlens, slots, fresh, out, H, dk, dv, k_scale, single_tokens);
   return cuda_status("retention");
 }
 
@@ -385,7 +445,9 @@ DINFER_API int dinfer_retention_chunks(const float* q, const float* k, const flo
   ChunkParams p{q, k, v, ldq, ldk, ldv, powers, state, ld_state, cu_seqlens, slots, fresh, out, work, H, dk, dv, k_scale};
   launch_pdl(retention_sums_kernel, dim3(chunks, H * tiles_k * tiles_v, B), dim3(THREADS), 0, stream, p);
   const int64_t total = (int64_t)H * dk * dv;
-  launch_pdl(retention_scan_kernel, dim3((unsigned)((total + THREADS - 1) / THREADS), B), dim3(THREADS), 0, stream, p);
+  const bool vec = dv % 4 == 0 && ld_state % 4 == 0 && (uintptr_t)state % 16 == 0 && (uintptr_t)work % 16 == 0;
+  if (vec) launch_pdl(retention_scan_kernel<4>, dim3((unsigned)((total / 4 + THREADS - 1) / THREADS), B), dim3(THREADS), 0, stream, p);
+  else launch_pdl(retention_scan_kernel<1>, dim3((unsigned)((total + THREADS - 1) / THREADS), B), dim3(THREADS), 0, stream, p);
   launch_pdl(retention_outputs_kernel, dim3(chunks, H * tiles_v, B), dim3(THREADS), 0, stream, p);
   return cuda_status("retention_chunks");
 }

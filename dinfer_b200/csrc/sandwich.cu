@@ -143,7 +143,8 @@ DINFER_API int dinfer_gain_norm_join(const void* a, int64_t lda, float g_a, cons
                          (uintptr_t)x_in % 16 == 0 && (uintptr_t)x_out % 16 == 0 && (uintptr_t)first % 16 == 0 &&
                          (uintptr_t)results % 16 == 0 && (uintptr_t)avg_out % 16 == 0 && (uintptr_t)next_out % 16 == 0;
         auto k = vec ? gain_norm_join_vec_kernel<TA, TO, TW> : gain_norm_join_kernel<TA, TO, TW>;
-        const int threads = vec ? min(1024, ((h / 4 + 31) / 32) * 32) : 256;
+        // few rows: the whole row at once; many rows: smaller CTAs, so that several rows' phases overlap on an SM
+        const int threads = vec ? min(T >= 512 ? 256 : 1024, ((h / 4 + 31) / 32) * 32) : 256;
         if (smem > 48 * 1024) {
           cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
           if (e != cudaSuccess) return refuse((int)e, "gain_norm_join: shared memory opt-in failed: %s", cudaGetErrorString(e));

@@ -145,8 +145,8 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
         return out
     lib, f = _fn("retention", "dinfer_retention",
                  [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
-                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(powers), ptr(state), state.stride(0),
                  ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), B, H, dk, dv, float(k_scale),
-                 stream_handle()), "retention")
+                 int(max_q_len == 1 and T == B), stream_handle()), "retention")
     return out
