@@ -20,12 +20,13 @@ def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (32, 64, 128) and 1 <= group <= 16
 
 
-def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """Key splits of the decode shape.  Two CTAs fit an SM: with few (request, kv head) pairs the
+def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int, ctas_per_sm: int = 2) -> int:
+    """Key splits of the decode shape.  Two CTAs fit an SM (``ctas_per_sm``; one for the differential kernel):
+    with few (request, kv head) pairs the
     splits fill those slots in one wave; with as many pairs as slots or more, splitting only adds
     partial sums to fold, so there is none.  Never more than a quarter of the 64-key tiles, at
     most 16 (the largest cluster)."""
-    slots = 2 * num_sms()
+    slots = ctas_per_sm * num_sms()
     base = max(1, num_reqs * num_kv_heads)
     want = slots // base if base <= slots else 1
     tiles = max(1, (max_seq_len + 63) // 64)

@@ -34,7 +34,7 @@ from .spec import TensorDecl
 class DifferentialAttention(Mixer):
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim`` (of one map), ``v_dim``, ``scale``, ``diff`` (the constant in
     lambda and in the output factor ``1 - diff``), ``eps`` (of the output norm), optional ``window``, ``keep_first``,
-    ``cache_block_size``, ``out_float32``, and the tensor names ``q_proj``, ``k_proj``, ``v_proj``, ``gate_proj`` ([H,
+    ``cache_block_size``, ``out_float32``, ``decode_splits`` (key splits of decoded tokens; 0: chosen per step), and the tensor names ``q_proj``, ``k_proj``, ``v_proj``, ``gate_proj`` ([H,
     width]), ``o_proj``, ``lambda_q1``, ``lambda_k1``, ``lambda_q2``, ``lambda_k2`` ([head_dim] each)."""
 
     def __init__(self, params, env: BuildEnv, prefix=""):
@@ -50,6 +50,7 @@ class DifferentialAttention(Mixer):
         self.eps = float(p.get("eps", 1e-6))
         self.window = p.get("window")
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.force_splits = int(p.get("decode_splits") or 0)
         self.page_size = p.get("cache_block_size")
         self.out_float32 = bool(p.get("out_float32", False))
         n = lambda key, default: prefix + p.get(key, default)
@@ -99,8 +100,11 @@ class DifferentialAttention(Mixer):
         q, gate, window = P[:, :nq], P[:, nq + nk + nv:nq + nk + nv + H], int(self.window or 0)
         if attention_ops.diff_tc_supported(P.dtype, D, Dv, H // G):
             # the keys a decoded token sees end at the window (and the kept first ones): no more splits than they fill
-            seen = min(ctx.max_seq_len, window + self.keep_first) if window else ctx.max_seq_len
-            splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, G, seen)
+            # (inside a captured graph the count is fixed for the longest request the engine admits).  One CTA of the
+            # decode shape fits an SM, so the splits are counted against one wave of as many CTAs as SMs.
+            longest = self.env.max_positions if ctx.decode_splits else ctx.max_seq_len
+            seen = min(longest, window + self.keep_first) if window else longest
+            splits = self.force_splits or attention_ops.decode_splits(ctx.num_reqs, G, seen, ctas_per_sm=1)
             attention_ops.attention_diff_tc(q, out, gate, cache.kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, H, G, D, Dv,
                                             self.scale, window, self.keep_first, self.lam, self.eps, 1.0 - self.diff,
                                             ctx.max_q_len, ctx.any_decode, ctx.any_prefill, splits)

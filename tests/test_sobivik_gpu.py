@@ -79,7 +79,7 @@ class Bench:
         from dinfer_b200.parts.base import MIXERS, CacheBinding, split_needs
         self.dt = DT[dtype]
         self.splits = splits                                # > 0: decoded tokens' keys are cut into this many parts
-        self.part = MIXERS.get(kind)(params, env(width, self.dt), "")
+        self.part = MIXERS.get(kind)(dict(params, decode_splits=splits) if splits else params, env(width, self.dt), "")
         names = {d.name for d in self.part.declare()}
         assert names == set(W), (sorted(names), sorted(W))
         self.part.bind({k: dev(v, self.dt) for k, v in W.items()})
