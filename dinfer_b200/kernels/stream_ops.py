@@ -128,8 +128,11 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
         raise KernelError("retention: powers float32 [H, 65]")
     require_cuda(powers)
     B = cu_seqlens.numel() - 1
+    single = max_q_len == 1 and T == B
     if side_by_side is None:
-        side_by_side = max_q_len > RETENTION_CHAIN_TOKENS
+        # the chain keeps a chunk's q and k and a slice of S in shared memory: keys too wide for that go side by side
+        chain_smem = 4 * (2 * 32 * (dk + 1) + dk * 32 + 2 * 32 * 32 + 32 * 33 + 33)
+        side_by_side = max_q_len > RETENTION_CHAIN_TOKENS or (not single and chain_smem > 200 * 1024)
     if side_by_side:
         longest = int(max_q_len) if max_q_len > 0 else T
         lib, f = _fn("retention", "dinfer_retention_chunks",
@@ -148,5 +151,5 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     check(lib, f(ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(powers), ptr(state), state.stride(0),
                  ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), B, H, dk, dv, float(k_scale),
-                 int(max_q_len == 1 and T == B), stream_handle()), "retention")
+                 int(single), stream_handle()), "retention")
     return out

@@ -196,10 +196,11 @@ def test_short_conv_input(dtype, taps, width):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H_, dk, dv, width", [(2, 16, 24, 64), (3, 128, 40, 96), (1, 12, 20, 72), (4, 64, 64, 128), (5, 33, 7, 40),
-                                               (2, 256, 96, 64)])
+                                               (2, 256, 96, 64), (1, 520, 24, 64)])
 def test_retention(dtype, H_, dk, dv, width):
     """The part against the recurrence written out token by token: batches of unequal requests, portions of one and
-    two tokens and of more than a chunk, state rows that another request held before."""
+    two tokens and of more than a chunk, state rows that another request held before, a key too wide for the form that
+    keeps a chunk in shared memory."""
     decay = [1.0 - 0.3 ** (i + 1) for i in range(H_)]
     p = {"num_heads": H_, "key_dim": dk, "value_dim": dv, "decay": decay, "eps": 1e-5}
     import dinfer_b200.models.decoder  # noqa: F401
