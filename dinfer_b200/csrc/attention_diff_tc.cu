@@ -213,7 +213,9 @@ __global__ void __launch_bounds__(NT, DECODE ? 1 : 2) attention_diff_tc_kernel(c
     }
     // scale into the exp2 domain and mask by position
     const int jbase = tile_of(t) * BN + key_off;
-    const bool need_mask = (jbase + NK - 1 > hist + first_tok) || (p.window > 0) || DECODE;
+    // a tile needs no mask when every row of the CTA sees all of it: it ends at or before the first row's position and
+    // begins inside the last row's window (the kept first tokens' tiles always take the mask)
+    const bool need_mask = DECODE || (jbase + NK - 1 > hist + first_tok) || (p.window > 0 && jbase <= hist + last_tok - p.window);
 #pragma unroll
     for (int i = 0; i < NK / 8; ++i) {
 #pragma unroll
