@@ -47,6 +47,11 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
 }
+__device__ __forceinline__ float fast_exp2(float x) {     // ex2.approx: -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
@@ -239,18 +244,20 @@ __global__ void __launch_bounds__(NT, DECODE ? 1 : 2) attention_diff_tc_kernel(c
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_use = mx == -INFINITY ? 0.f : mx;
-      const float alpha = exp2f(m_run[r] - m_use);          // 0 when nothing was seen before
+      const float alpha = fast_exp2(m_run[r] - m_use);      // 0 when nothing was seen before
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < NK / 8; ++i) {
-        s[i][2 * r] = exp2f(s[i][2 * r] - m_use);
-        s[i][2 * r + 1] = exp2f(s[i][2 * r + 1] - m_use);
+        s[i][2 * r] = fast_exp2(s[i][2 * r] - m_use);
+        s[i][2 * r + 1] = fast_exp2(s[i][2 * r + 1] - m_use);
         sum += s[i][2 * r] + s[i][2 * r + 1];
       }
       l_run[r] = l_run[r] * alpha + sum;
       m_run[r] = mx;
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {           // after the first tiles a row's maximum seldom grows
 #pragma unroll
-      for (int i = 0; i < DV / 8; ++i) { o[i][2 * r] *= alpha; o[i][2 * r + 1] *= alpha; }
+        for (int i = 0; i < DV / 8; ++i) { o[i][2 * r] *= alpha; o[i][2 * r + 1] *= alpha; }
+      }
     }
     // O += P V
 #pragma unroll
