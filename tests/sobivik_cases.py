@@ -64,10 +64,10 @@ SOBIVIK_C = model(331, 72, 1e-6, 0.7, 1.0, 1, [
 SOBIVIK_D = model(257, 100, 2e-6, 8.0, 0.25, 5, [
     layer(retention(5, 12, 12, (0.9, 0.95, 0.99, 0.999, 0.9999)), 36),
     layer(retention(2, 40, 36, (0.999, 0.8)), None)])
-# sizes of real layers in small: heads of 64 and 128, a latent of 128
-SOBIVIK_E = model(400, 256, 1e-5, 16.0, 1.5, 3, [
-    layer(retention(4, 64, 64, (0.97, 0.99, 0.997, 0.9995)), 320),
-    layer(differential(4, 2, 64, 128, 64, 4, 0.5), 256),
+# sizes of real layers in small: heads of 64 and 128, a latent of 128, six taps
+SOBIVIK_E = model(400, 384, 5e-6, 12.0, 1.5, 6, [
+    layer(retention(3, 64, 128, (0.97, 0.99, 0.9995)), 448),
+    layer(differential(4, 2, 64, 128, 64, 4, 0.25), 256),
     layer(latent(8, 64, 64, 64, 128, 96, 100, base=5000.0, scaling=(2.0, 128, 32.0, 1.0)), 128)])
 CONFIGS = {"A": SOBIVIK_A, "B": SOBIVIK_B, "C": SOBIVIK_C, "D": SOBIVIK_D, "E": SOBIVIK_E}
 

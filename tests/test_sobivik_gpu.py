@@ -195,7 +195,7 @@ def test_short_conv_input(dtype, taps, width):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H_, dk, dv, width", [(2, 16, 24, 64), (3, 128, 40, 96), (1, 12, 20, 72), (4, 64, 64, 128), (5, 33, 7, 40),
+@pytest.mark.parametrize("H_, dk, dv, width", [(2, 16, 24, 64), (3, 128, 40, 96), (1, 12, 20, 72), (6, 64, 64, 128), (5, 33, 7, 40),
                                                (2, 256, 96, 64), (1, 520, 24, 64)])
 def test_retention(dtype, H_, dk, dv, width):
     """The part against the recurrence written out token by token: batches of unequal requests, portions of one and
@@ -319,7 +319,7 @@ def test_latent_attention_window_sink_gate(dtype, H_, D, Pr, V, R, Rq, window, r
 
 # the last five have sizes that the tensor-core kernel takes in bfloat16 (maps of 32, 64, 128; values of 64, 128)
 DIFF = [(4, 2, 8, 16, 9, 3, 16), (6, 1, 24, 40, 7, 0, 16), (3, 3, 10, 6, 1, 5, 4), (9, 3, 6, 14, 40, 17, 8), (2, 2, 32, 32, 200, 70, 16),
-        (4, 2, 64, 128, 64, 4, 64), (4, 2, 32, 64, 40, 5, 16), (8, 1, 32, 64, 30, 70, 8), (2, 2, 128, 64, 50, 3, 32), (3, 1, 64, 64, 1, 2, 4)]
+        (4, 2, 64, 128, 64, 4, 64), (6, 2, 32, 64, 40, 5, 16), (8, 1, 32, 64, 30, 70, 8), (2, 2, 128, 64, 50, 3, 32), (3, 1, 64, 64, 1, 2, 4)]
 
 
 def diff_case(dtype, H_, G, D, V, window, keep, block_size, inputs=None, tie=False, width=64, plan=PLAN, seed=0, splits=0):
@@ -356,13 +356,13 @@ def test_differential_attention_decodes_with_split_keys(splits):
     g = torch.Generator().manual_seed(11)
     rows = {"a": torch.randn(420, 64, generator=g).to(torch.bfloat16).float(), "b": torch.randn(9, 64, generator=g).to(torch.bfloat16).float()}
     plan = [{"a": 400, "b": 3}] + [{"a": 1, "b": 1}] * 6 + [{"a": 14}]
-    got, want = diff_case("bfloat16", 4, 2, 32, 64, 150, 70, 16, inputs=rows, plan=plan, splits=splits)
+    got, want = diff_case("bfloat16", 6, 3, 32, 64, 150, 70, 16, inputs=rows, plan=plan, splits=splits)
     for r in want:
         close(got[r], want[r], "bfloat16", r)
 
 
 # sizes for the plain-arithmetic kernel (32-bit) and for the tensor-core kernel (bfloat16)
-EDGE_SIZES = {"float32": (4, 2, 16, 24), "bfloat16": (4, 2, 32, 64)}
+EDGE_SIZES = {"float32": (4, 2, 16, 24), "bfloat16": (6, 3, 32, 64)}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
