@@ -107,7 +107,7 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
 }
 
 template <int D, int DV, bool DECODE>
-__global__ void __launch_bounds__(NT, DECODE ? 1 : 2) attention_diff_tc_kernel(const Params p) {
+__global__ void __launch_bounds__(NT, 2) attention_diff_tc_kernel(const Params p) {
   constexpr int DK = 2 * D;
   constexpr int STAGES = DECODE ? STAGES_DECODE : STAGES_PROMPT;
   constexpr int QROWS = DECODE ? 16 : BMP;

@@ -21,7 +21,7 @@ def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
 
 
 def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int, ctas_per_sm: int = 2) -> int:
-    """Key splits of the decode shape.  Two CTAs fit an SM (``ctas_per_sm``; one for the differential kernel):
+    """Key splits of the decode shape.  ``ctas_per_sm`` CTAs fit an SM (two of the attention kernels; the differential kernel says how many of its own):
     with few (request, kv head) pairs the
     splits fill those slots in one wave; with as many pairs as slots or more, splitting only adds
     partial sums to fold, so there is none.  Never more than a quarter of the 64-key tiles, at
@@ -249,6 +249,14 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_
 
 def diff_tc_supported(dtype: torch.dtype, head_dim: int, v_dim: int, group: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (32, 64, 128) and v_dim in (64, 128) and 1 <= group <= 16
+
+
+def diff_tc_decode_ctas_per_sm(head_dim: int, v_dim: int) -> int:
+    """How many CTAs of the differential kernel's decode shape an SM holds (128 registers a thread allow two; the
+    three stages of 64 keys with both maps and the values, or the fold buffers, decide)."""
+    tiles = (16 * 2 * head_dim + 3 * 64 * (2 * head_dim + v_dim)) * 2
+    fold = (8 * 16 * v_dim + 2 * 8 * 16) * 4
+    return 2 if 2 * (max(tiles, fold) + 4096) <= 227 * 1024 else 1
 
 
 def attention_diff_tc(q: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], cache: torch.Tensor,

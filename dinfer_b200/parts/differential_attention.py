@@ -100,11 +100,12 @@ class DifferentialAttention(Mixer):
         q, gate, window = P[:, :nq], P[:, nq + nk + nv:nq + nk + nv + H], int(self.window or 0)
         if attention_ops.diff_tc_supported(P.dtype, D, Dv, H // G):
             # the keys a decoded token sees end at the window (and the kept first ones): no more splits than they fill
-            # (inside a captured graph the count is fixed for the longest request the engine admits).  One CTA of the
-            # decode shape fits an SM, so the splits are counted against one wave of as many CTAs as SMs.
+            # (inside a captured graph the count is fixed for the longest request the engine admits).  The splits are
+            # counted against one wave of the CTAs of the decode shape that fit the SMs.
             longest = self.env.max_positions if ctx.decode_splits else ctx.max_seq_len
             seen = min(longest, window + self.keep_first) if window else longest
-            splits = self.force_splits or attention_ops.decode_splits(ctx.num_reqs, G, seen, ctas_per_sm=1)
+            splits = self.force_splits or attention_ops.decode_splits(ctx.num_reqs, G, seen,
+                                                                      attention_ops.diff_tc_decode_ctas_per_sm(D, Dv))
             attention_ops.attention_diff_tc(q, out, gate, cache.kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, H, G, D, Dv,
                                             self.scale, window, self.keep_first, self.lam, self.eps, 1.0 - self.diff,
                                             ctx.max_q_len, ctx.any_decode, ctx.any_prefill, splits)
