@@ -430,7 +430,7 @@ DINFER_API int64_t dinfer_retention_work_floats(int64_t T, int B, int H, int dk,
   return (T / CP + B) * (int64_t)H * dk * dv;
 }
 
-// The same contract as dinfer_retention, for steps whose longest portion has max_q_len tokens: chunks of 64 tokens side
+// The same arguments and results as dinfer_retention, for steps whose longest portion has max_q_len tokens: chunks of 64 tokens side
 // by side.  work: dinfer_retention_work_floats() floats.
 DINFER_API int dinfer_retention_chunks(const float* q, const float* k, const float* v, int64_t ldq, int64_t ldk, int64_t ldv,
                                        const float* powers, float* state, int64_t ld_state, const int* cu_seqlens,
