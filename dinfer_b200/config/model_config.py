@@ -715,3 +715,180 @@ class SobivikConfig:
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids)
         return d
+
+
+# ---------------------------------------------------------------- Porovik
+
+def _positive(s, fields, where: str) -> None:
+    for f in fields:
+        if getattr(s, f) <= 0:
+            raise ConfigError(f"config.json: {where}'{f}' must be positive, got {getattr(s, f)}")
+
+
+@dataclass(frozen=True)
+class GateWriteSizes:
+    """An ``hgrn2`` mixer: ``heads`` heads of ``dim`` query / forget-gate channels and ``vdim`` value channels."""
+    heads: int
+    dim: int
+    vdim: int
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "GateWriteSizes":
+        dim = _take(m, "dim", int)
+        s = cls(heads=_take(m, "heads", int), dim=dim, vdim=_take(m, "vdim", int, dim))
+        _positive(s, ("heads", "dim", "vdim"), where)
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "vdim": self.vdim}
+
+
+@dataclass(frozen=True)
+class GeneralDeltaSizes:
+    """A ``general_delta`` mixer: ``heads`` heads of ``dim`` key channels (values as wide unless ``vdim`` says
+    otherwise); the thin middle of the decay's projection is whatever the weight file holds (``decay_rank`` names it
+    for weights that are drawn, not read)."""
+    heads: int
+    dim: int
+    vdim: int
+    decay_rank: int = -1
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "GeneralDeltaSizes":
+        dim = _take(m, "dim", int)
+        s = cls(heads=_take(m, "heads", int), dim=dim, vdim=_take(m, "vdim", int, dim),
+                decay_rank=_take(m, "decay_rank", int, -1))
+        _positive(s, ("heads", "dim", "vdim"), where)
+        if s.decay_rank == 0 or s.decay_rank < -1:
+            raise ConfigError(f"config.json: {where}'decay_rank' must be positive where it is given")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = {"heads": self.heads, "dim": self.dim}
+        if self.vdim != self.dim:
+            d["vdim"] = self.vdim
+        if self.decay_rank > 0:
+            d["decay_rank"] = self.decay_rank
+        return d
+
+
+@dataclass(frozen=True)
+class BiasedAttentionSizes:
+    """An ``attention`` mixer of Porovik: grouped heads without a rotation, a query temperature that grows with the
+    position (``q_temp.coef``, ``q_temp.every``; absent: none), a distance bias per head, values that may be mixed
+    with an earlier layer's (``v_mix``) and a sigmoid gate on the heads."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    temp_coef: float = 0.0
+    temp_every: int = 1
+    v_mix: bool = False
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "BiasedAttentionSizes":
+        heads, dim = _take(m, "heads", int), _take(m, "dim", int)
+        qt = _section(m, "q_temp", where, optional=True)
+        s = cls(heads=heads, kv_heads=_take(m, "kv_heads", int, heads), dim=dim, vdim=_take(m, "vdim", int, dim),
+                scale=_take(m, "scale", float), temp_coef=_take(qt, "coef", float) if qt else 0.0,
+                temp_every=_take(qt, "every", int) if qt else 1, v_mix=_take(m, "v_mix", bool, False))
+        _positive(s, ("heads", "kv_heads", "dim", "vdim", "temp_every"), where)
+        if s.heads % s.kv_heads:
+            raise ConfigError(f"config.json: {where}heads {s.heads} must be a multiple of kv_heads {s.kv_heads}")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
+             "v_mix": self.v_mix}
+        if self.temp_coef != 0.0:
+            d["q_temp"] = {"coef": self.temp_coef, "every": self.temp_every}
+        return d
+
+
+@dataclass(frozen=True)
+class BigramHash:
+    """The hashed bigram table of the embedding: row ``(previous * mul_prev + current * mul_cur) mod buckets``, and row
+    ``buckets`` for a sequence's first token."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
+class PorovikLayer:
+    type: str
+    mixer: Any
+    mlp: Optional[FeedForwardSizes]      # None: the layer has no feed-forward
+
+
+@dataclass(frozen=True)
+class PorovikConfig:
+    """``config.json`` of a Porovik model: ``vocab``, ``width``, ``max_positions`` (rows of the learned position
+    table), ``norm.eps``, ``embedding.bigram.{buckets, mul_prev, mul_cur}`` and the list ``layers``, each entry with
+    its ``type`` (``hgrn2``, ``general_delta`` or ``attention``), the mixer's sizes and its feed-forward (``mlp``:
+    dense, a mixture of experts, or null)."""
+    vocab: int
+    width: int
+    norm_eps: float
+    max_positions: int
+    bigram: Optional[BigramHash]
+    layers: Tuple[PorovikLayer, ...]
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Porovik"
+
+    MIXER_TYPES = {"hgrn2": GateWriteSizes, "general_delta": GeneralDeltaSizes, "attention": BiasedAttentionSizes}
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "PorovikConfig":
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, l in enumerate(raw):
+            where = f"layers[{i}]: "
+            if not isinstance(l, dict):
+                raise ConfigError(f"config.json: {where}must be an object")
+            kind = _take(l, "type", str)
+            if kind not in cls.MIXER_TYPES:
+                raise ConfigError(f"config.json: {where}unknown type {kind!r} ({', '.join(cls.MIXER_TYPES)})")
+            mixer = cls.MIXER_TYPES[kind].from_dict(_section(l, "mixer", where), where)
+            mlp = _section(l, "mlp", where, optional=True)
+            ff = FeedForwardSizes.from_dict(mlp, where) if mlp else None
+            if ff is not None and ff.shared_ff:
+                raise ConfigError(f"config.json: {where}the design's mixture of experts has no shared expert")
+            layers.append(PorovikLayer(kind, mixer, ff))
+        emb = _section(d, "embedding", "", optional=True) or {}
+        bg = _section(emb, "bigram", "embedding: ", optional=True)
+        bigram = BigramHash(_take(bg, "buckets", int), _take(bg, "mul_prev", int), _take(bg, "mul_cur", int)) if bg else None
+        if bigram is not None and (bigram.buckets <= 0 or bigram.mul_prev < 0 or bigram.mul_cur < 0):
+            raise ConfigError("config.json: embedding.bigram: buckets must be positive, the multipliers not negative")
+        eos = d.get("eos_token_id")
+        eos_ids = (eos,) if isinstance(eos, int) and not isinstance(eos, bool) else \
+            tuple(int(x) for x in eos) if isinstance(eos, (list, tuple)) else ()
+        cfg = cls(vocab=_take(d, "vocab", int), width=_take(d, "width", int),
+                  norm_eps=_take(_section(d, "norm", ""), "eps", float), max_positions=_take(d, "max_positions", int),
+                  bigram=bigram, layers=tuple(layers), eos_token_ids=eos_ids,
+                  architecture=str(d.get("architecture") or (d.get("architectures") or ["Porovik"])[0]))
+        if cfg.vocab <= 0 or cfg.width <= 0 or cfg.max_positions <= 1:
+            raise ConfigError("config.json: vocab and width must be positive, max_positions at least 2")
+        if not cfg.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {cfg.norm_eps}")
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        def mlp(f):
+            if f is None:
+                return None
+            if f.kind == "dense":
+                return {"kind": "dense", "ff": f.ff}
+            return {"kind": "moe", "expert": {"ff": f.ff}, "router": {"experts": f.experts, "top": f.top}}
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+             "max_positions": self.max_positions,
+             "layers": [{"type": l.type, "mixer": l.mixer.to_dict(), "mlp": mlp(l.mlp)} for l in self.layers]}
+        if self.bigram is not None:
+            d["embedding"] = {"bigram": {"buckets": self.bigram.buckets, "mul_prev": self.bigram.mul_prev,
+                                         "mul_cur": self.bigram.mul_cur}}
+        if self.eos_token_ids:
+            d["eos_token_id"] = list(self.eos_token_ids)
+        return d

@@ -64,4 +64,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import dobedra, qwen3, sobivik, zasipel  # noqa: F401  (register themselves)
+        from ..models import dobedra, porovik, qwen3, sobivik, zasipel  # noqa: F401  (register themselves)

@@ -7,7 +7,8 @@
 // 32-bit (expf, not the fast intrinsic).  A query at position p sees the keys [max(0, p-window+1), p]
 // of its own request, read through the request's block table.  Values may be Dv wide where keys are D wide (the
 // cache's rows are then Dc = max(D, Dv) wide); with `sink` the softmax has one more term of score 0 and no value:
-// p_j = exp(s_j) / (1 + sum exp(s_j)).
+// p_j = exp(s_j) / (1 + sum exp(s_j)).  With `slopes` (one number per query head) a distance bias is taken off every
+// score: s_ij - slopes[h] * (i - j).
 //
 // Counterpart in the reference: the any-D reference kernels crates/kernels/cuda/gqa.cu:956-1118.
 #include "common.cuh"
@@ -25,7 +26,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
                          const T* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                          int num_reqs, int H, int Hkv, int D, int Dv, int Dc, int block_size, float scale, int window,
-                         int sink) {
+                         int sink, const float* __restrict__ slopes) {
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * WARPS + warp;
@@ -40,6 +41,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
   const int hk = h / (H / Hkv);
   const int pos = positions[t];
   const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const float slope = slopes ? slopes[h] : 0.f;
 
   float qv[C], acc[C];
 #pragma unroll
@@ -70,7 +72,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
       }
     }
 #pragma unroll
-    for (int u = 0; u < KEYS; ++u) s[u] = kp[u] ? warp_sum(s[u]) : -INFINITY;
+    for (int u = 0; u < KEYS; ++u) s[u] = kp[u] ? warp_sum(s[u]) - slope * (float)(pos - (j0 + u)) : -INFINITY;
     float m_new = m;
 #pragma unroll
     for (int u = 0; u < KEYS; ++u) m_new = fmaxf(m_new, s[u]);
@@ -112,11 +114,12 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
 template <typename T, int C>
 int launch(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache, const int* block_table,
            int max_blocks, const int* cu_seqlens, const int* positions, int T_, int B, int H, int Hkv,
-           int D, int Dv, int Dc, int block_size, float scale, int window, int sink, cudaStream_t stream) {
+           int D, int Dv, int Dc, int block_size, float scale, int window, int sink, const float* slopes,
+           cudaStream_t stream) {
   dim3 grid(T_, (H + WARPS - 1) / WARPS);
   attention_generic_kernel<T, C><<<grid, WARPS * 32, 0, stream>>>(
       (const T*)q, ldq, (T*)out, ldo, (const T*)cache, block_table, max_blocks, cu_seqlens, positions,
-      B, H, Hkv, D, Dv, Dc, block_size, scale, window, sink);
+      B, H, Hkv, D, Dv, Dc, block_size, scale, window, sink, slopes);
   return cuda_status("attention_generic");
 }
 
@@ -124,11 +127,11 @@ int launch(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache
 
 DINFER_DEFINE_LAST_ERROR()
 
-DINFER_API int dinfer_attention_generic_ex(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
-                                           const int* block_table, int max_blocks, const int* cu_seqlens,
-                                           const int* positions, int T, int B, int H, int Hkv, int D, int Dv, int Dc,
-                                           int block_size, float scale, int window, int sink, int dtype,
-                                           cudaStream_t stream);
+DINFER_API int dinfer_attention_generic_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                             const int* block_table, int max_blocks, const int* cu_seqlens,
+                                             const int* positions, int T, int B, int H, int Hkv, int D, int Dv, int Dc,
+                                             int block_size, float scale, int window, int sink, const float* slopes,
+                                             int dtype, cudaStream_t stream);
 
 // q: [T, ...] rows of stride ldq, head h at h*D; out likewise with stride ldo.
 // cache [num_blocks, 2, Hkv, block_size, D]; block_table [B, max_blocks] int32;
@@ -139,8 +142,8 @@ DINFER_API int dinfer_attention_generic(const void* q, int64_t ldq, void* out, i
                                         const int* positions, int T, int B, int H, int Hkv, int D,
                                         int block_size, float scale, int window, int dtype,
                                         cudaStream_t stream) {
-  return dinfer_attention_generic_ex(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, positions, T, B, H,
-                                     Hkv, D, D, D, block_size, scale, window, 0, dtype, stream);
+  return dinfer_attention_generic_bias(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, positions, T, B, H,
+                                       Hkv, D, D, D, block_size, scale, window, 0, nullptr, dtype, stream);
 }
 
 // The same with values Dv wide in a cache whose rows are Dc wide (out: head h at h*Dv), and an optional sink.
@@ -149,6 +152,16 @@ DINFER_API int dinfer_attention_generic_ex(const void* q, int64_t ldq, void* out
                                            const int* positions, int T, int B, int H, int Hkv, int D, int Dv, int Dc,
                                            int block_size, float scale, int window, int sink, int dtype,
                                            cudaStream_t stream) {
+  return dinfer_attention_generic_bias(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, positions, T, B, H,
+                                       Hkv, D, Dv, Dc, block_size, scale, window, sink, nullptr, dtype, stream);
+}
+
+// The same with a distance bias: slopes [H] f32 or null.
+DINFER_API int dinfer_attention_generic_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                             const int* block_table, int max_blocks, const int* cu_seqlens,
+                                             const int* positions, int T, int B, int H, int Hkv, int D, int Dv, int Dc,
+                                             int block_size, float scale, int window, int sink, const float* slopes,
+                                             int dtype, cudaStream_t stream) {
   if (Dv <= 0 || Dc < D || Dc < Dv) return refuse(DINFER_BAD_ARGUMENT, "attention_generic: bad sizes D=%d Dv=%d Dc=%d", D, Dv, Dc);
   if (T < 0 || B <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || block_size <= 0 || max_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_generic: bad sizes T=%d B=%d H=%d Hkv=%d D=%d block=%d",
@@ -159,7 +172,7 @@ DINFER_API int dinfer_attention_generic_ex(const void* q, int64_t ldq, void* out
   if (T == 0) return 0;
   const int c = ((D > Dv ? D : Dv) + 31) / 32;
 #define GO(C) return launch<T_, C>(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, positions, \
-                                   T, B, H, Hkv, D, Dv, Dc, block_size, scale, window, sink, stream)
+                                   T, B, H, Hkv, D, Dv, Dc, block_size, scale, window, sink, slopes, stream)
   DINFER_DISPATCH_DTYPE(dtype, T_, {
     if (c <= 1) GO(1);
     else if (c <= 2) GO(2);

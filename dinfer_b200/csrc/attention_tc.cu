@@ -40,6 +40,7 @@ struct Params {
   int H, Hkv, group, block_size, window;
   int sink;                    // one more softmax term of score 0 without a value
   float scale_log2;            // scale * log2(e)
+  const float* slopes;         // [H] or null: a distance bias, score - slopes[h] * (i - j)
   int splits;                  // decode shape only
   float* part_o; float* part_ml;
 };
@@ -183,6 +184,14 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
     const int row = row0 + wrow + g + 8 * i;
     pos_r[i] = row < rows_total ? hist + row / p.group : -1;
   }
+  float slope_r[2] = {0.f, 0.f};                           // the rows' slopes, in the exp2 domain
+  if (p.slopes) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + wrow + g + 8 * i;
+      if (row < rows_total) slope_r[i] = p.slopes[hk * p.group + row % p.group] * 1.4426950408889634f;
+    }
+  }
   constexpr int NK = DECODE ? 16 : BN;                     // keys of a tile this warp works on
   const int key_off = DECODE ? warp * 16 : 0;
 
@@ -230,6 +239,7 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float v = s[i][e] * p.scale_log2;
+        if (p.slopes) v -= slope_r[e >> 1] * (float)(pos_r[e >> 1] - (jbase + i * 8 + tq * 2 + (e & 1)));
         if (need_mask) {
           const int j = jbase + i * 8 + tq * 2 + (e & 1);
           const int pr = pos_r[e >> 1];
@@ -420,11 +430,12 @@ DINFER_API int64_t dinfer_attention_tc_scratch_floats(int B, int H, int D, int s
 // any_decode / any_prefill: whether the batch holds requests with q_len == 1 / q_len > 1.
 // scratch: dinfer_attention_tc_scratch_floats() floats, or null when splits == 1.
 // sink != 0: the softmax has one more term of score 0 that carries no value (p_j = exp(s_j) / (1 + sum exp(s_j))).
-DINFER_API int dinfer_attention_tc_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+// slopes: f32 [H] or null; with them score_ij - slopes[h] * (i - j).
+DINFER_API int dinfer_attention_tc_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
                                         const int* block_table, int max_blocks, const int* cu_seqlens,
                                         const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
-                                        float scale, int window, int sink, int max_q_len, int any_decode,
-                                        int any_prefill, int splits, float* scratch, cudaStream_t stream) {
+                                        float scale, int window, int sink, const float* slopes, int max_q_len,
+                                        int any_decode, int any_prefill, int splits, float* scratch, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || block_size <= 0 || max_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_tc: bad sizes B=%d H=%d Hkv=%d block=%d", B, H, Hkv, block_size);
   if (!dinfer_attention_tc_supports(D, H / Hkv))
@@ -438,11 +449,22 @@ DINFER_API int dinfer_attention_tc_sink(const void* q, int64_t ldq, void* out, i
   p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.max_blocks = max_blocks;
   p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = H / Hkv;
   p.block_size = block_size; p.window = window; p.sink = sink; p.scale_log2 = scale * 1.4426950408889634f;
+  p.slopes = slopes;
   p.splits = splits; p.part_o = scratch;
   p.part_ml = scratch ? scratch + (int64_t)B * H * splits * D : nullptr;
   if (D == 32) return launch<32>(p, B, max_q_len, any_decode, any_prefill, stream);
   if (D == 64) return launch<64>(p, B, max_q_len, any_decode, any_prefill, stream);
   return launch<128>(p, B, max_q_len, any_decode, any_prefill, stream);
+}
+
+DINFER_API int dinfer_attention_tc_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                        const int* block_table, int max_blocks, const int* cu_seqlens,
+                                        const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
+                                        float scale, int window, int sink, int max_q_len, int any_decode,
+                                        int any_prefill, int splits, float* scratch, cudaStream_t stream) {
+  return dinfer_attention_tc_bias(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, seq_lens, B, H, Hkv, D,
+                                  block_size, scale, window, sink, nullptr, max_q_len, any_decode, any_prefill, splits,
+                                  scratch, stream);
 }
 
 DINFER_API int dinfer_attention_tc(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,

@@ -47,6 +47,7 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_diff": ("attention_diff.cu", []),
     "attention_diff_tc": ("attention_diff_tc.cu", []),
     "sandwich": ("sandwich.cu", []),
+    "linear_state": ("linear_state.cu", []),
     # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
     "host_core": ("host_core.cpp", []),
 }

@@ -375,11 +375,13 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
 }
 
 // ---------------------------------------------------------------- output norm and gate
-// one warp per (token, head): y = o * rsqrt(mean(o^2) + eps) * w * act(gate); the gate's values may be wider than y's
+// one warp per (token, head): y = o * rsqrt(mean(o^2) + eps) * w * act(gate); the gate's values may be wider than y's.
+// w_heads: the weight has an entry for every head's channel (H * dv) instead of one row (dv) shared by the heads;
+// gate may be null (no gate).
 template <typename TG, typename TA>
 __global__ void __launch_bounds__(128)
 delta_post_kernel(const float* __restrict__ o, const float* __restrict__ w, const TG* __restrict__ gate, int64_t ldg,
-                  TA* __restrict__ y, int64_t ldy, int T, int H, int dv, float eps, int sigmoid_gate) {
+                  TA* __restrict__ y, int64_t ldy, int T, int H, int dv, float eps, int sigmoid_gate, int w_heads) {
   pdl_enter();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t p = (int64_t)blockIdx.x * 4 + warp;
@@ -391,10 +393,14 @@ delta_post_kernel(const float* __restrict__ o, const float* __restrict__ w, cons
   for (int e = lane; e < dv; e += 32) ss += x[e] * x[e];
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)dv + eps);
+  const float* wh = w + (w_heads ? (int64_t)h * dv : 0);
   for (int e = lane; e < dv; e += 32) {
-    const float z = to_f32<TG>(gate[t * ldg + (int64_t)h * dv + e]);
-    const float a = sigmoid_gate ? sigmoid_f(z) : silu_f(z);
-    y[t * ldy + (int64_t)h * dv + e] = from_f32<TA>(x[e] * r * w[e] * a);
+    float a = 1.f;
+    if (gate) {
+      const float z = to_f32<TG>(gate[t * ldg + (int64_t)h * dv + e]);
+      a = sigmoid_gate ? sigmoid_f(z) : silu_f(z);
+    }
+    y[t * ldy + (int64_t)h * dv + e] = from_f32<TA>(x[e] * r * wh[e] * a);
   }
 }
 
@@ -507,16 +513,27 @@ DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const f
   return cuda_status("delta_recurrence");
 }
 
+DINFER_API int dinfer_delta_post_ex(const float* o, const float* w, const void* gate, int64_t ldg, void* y, int64_t ldy,
+                                    int T, int H, int dv, float eps, int sigmoid_gate, int w_heads, int gate_dtype,
+                                    int act_dtype, cudaStream_t stream);
+
 DINFER_API int dinfer_delta_post(const float* o, const float* w, const void* gate, int64_t ldg, void* y, int64_t ldy,
                                  int T, int H, int dv, float eps, int sigmoid_gate, int gate_dtype, int act_dtype,
                                  cudaStream_t stream) {
+  return dinfer_delta_post_ex(o, w, gate, ldg, y, ldy, T, H, dv, eps, sigmoid_gate, 0, gate_dtype, act_dtype, stream);
+}
+
+// w f32 [dv] (w_heads = 0) or [H * dv] (w_heads = 1); gate may be null.
+DINFER_API int dinfer_delta_post_ex(const float* o, const float* w, const void* gate, int64_t ldg, void* y, int64_t ldy,
+                                    int T, int H, int dv, float eps, int sigmoid_gate, int w_heads, int gate_dtype,
+                                    int act_dtype, cudaStream_t stream) {
   if (T < 0 || H <= 0 || dv <= 0) return refuse(DINFER_BAD_ARGUMENT, "delta_post: bad sizes T=%d H=%d dv=%d", T, H, dv);
   if (T == 0) return 0;
   const int64_t blocks = ((int64_t)T * H + 3) / 4;
   DINFER_DISPATCH_DTYPE(gate_dtype, TG,
     DINFER_DISPATCH_DTYPE(act_dtype, TA, {
       launch_pdl(delta_post_kernel<TG, TA>, dim3((unsigned)blocks), dim3(128), 0, stream, o, w, (const TG*)gate, ldg, (TA*)y,
-                 ldy, T, H, dv, eps, sigmoid_gate);
+                 ldy, T, H, dv, eps, sigmoid_gate, w_heads);
       return cuda_status("delta_post");
     }));
   return 0;

@@ -23,6 +23,65 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
   for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = to_f32<TW>(row[i]) * scale;
 }
 
+// The embedding of a design that adds a hashed bigram row and a learned position row to the token's own:
+//   out[t] = table[id] + bigram[(prev * mul_prev + id * mul_cur) mod buckets] + pos_table[positions[t]]
+// with `prev` the token before in the same request, and row `buckets` of the bigram table for a request's first token.
+// The token before the step's first one is part of the request's state: last[slots[b]] (nothing is read for a fresh
+// request).  A second kernel stores each request's last token of the step there.
+__device__ __forceinline__ int resolve_id(int id, const int* __restrict__ prev, int prev_rows, int vocab) {
+  if (id < 0 && prev != nullptr && -id - 1 < prev_rows) id = prev[-id - 1];
+  return (id < 0 || id >= vocab) ? 0 : id;
+}
+
+template <typename TW>
+__global__ void embedding_bigram_kernel(const int* __restrict__ ids, const int* __restrict__ prev, int prev_rows,
+                                        const TW* __restrict__ table, const TW* __restrict__ bigram,
+                                        const TW* __restrict__ pos_table, const int* __restrict__ positions,
+                                        const int* __restrict__ cu, const int* __restrict__ slots,
+                                        const int* __restrict__ fresh, const int* __restrict__ last, int B,
+                                        float* __restrict__ out, int h, int vocab, int buckets, int mul_prev, int mul_cur,
+                                        int max_pos) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int id = resolve_id(ids[t], prev, prev_rows, vocab);
+  const TW* row = table + (int64_t)id * h;
+  const TW* brow = nullptr;
+  if (bigram) {
+    int lo = 0, hi = B - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (cu[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    int before = -1;
+    if (t > cu[lo]) before = resolve_id(ids[t - 1], prev, prev_rows, vocab);
+    else if (!fresh[lo]) before = last[slots[lo]];
+    const int64_t r = before < 0 ? buckets : ((int64_t)before * mul_prev + (int64_t)id * mul_cur) % buckets;
+    brow = bigram + r * h;
+  }
+  const TW* prow = nullptr;
+  if (pos_table) {
+    int p = positions[t];
+    p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+    prow = pos_table + (int64_t)p * h;
+  }
+  float* o = out + (int64_t)t * h;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float v = to_f32<TW>(row[i]);
+    if (brow) v += to_f32<TW>(brow[i]);
+    if (prow) v += to_f32<TW>(prow[i]);
+    o[i] = v;
+  }
+}
+
+__global__ void last_token_kernel(const int* __restrict__ ids, const int* __restrict__ prev, int prev_rows,
+                                  const int* __restrict__ cu, const int* __restrict__ slots, int* __restrict__ last, int B,
+                                  int vocab) {
+  pdl_enter();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B || cu[b + 1] <= cu[b]) return;
+  last[slots[b]] = resolve_id(ids[cu[b + 1] - 1], prev, prev_rows, vocab);
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap) {
   pdl_enter();
   const float inv = 1.f / cap;
@@ -79,6 +138,25 @@ __global__ void gated_act_kernel(const T* __restrict__ x, T* __restrict__ out, i
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
     const float a = to_f32<T>(pairs ? row[2 * i] : row[i]);
     const float b = to_f32<T>(pairs ? row[2 * i + 1] : row[inter + i]);
+    o[i] = from_f32<T>(gate_activation(a, act) * b);
+  }
+}
+
+// the same with every row's inputs scaled first: out[t, i] = act(s_t gate_i) * (s_t up_i), s_t = scale[index[t]] (or
+// scale[t] without an index); an index outside [0, n_scale) gives a row of zeros.  For routed experts whose routing
+// weight multiplies the expert's input: a product is linear, so the weight is applied to its result.
+template <typename T>
+__global__ void gated_act_scaled_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int64_t ldx, int pairs,
+                                        int act, const float* __restrict__ scale, const int* __restrict__ index, int n_scale) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int at = index ? index[t] : t;
+  const float s = (at >= 0 && at < n_scale) ? scale[at] : 0.f;
+  const T* row = x + (int64_t)t * ldx;
+  T* o = out + (int64_t)t * inter;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
+    const float a = s * to_f32<T>(pairs ? row[2 * i] : row[i]);
+    const float b = s * to_f32<T>(pairs ? row[2 * i + 1] : row[inter + i]);
     o[i] = from_f32<T>(gate_activation(a, act) * b);
   }
 }
@@ -163,6 +241,47 @@ DINFER_API int dinfer_embedding(const int* ids, const int* prev, int prev_rows, 
   DINFER_DISPATCH_DTYPE(table_dtype, TW, {
     launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, prev, prev_rows, (const TW*)table, out, h, vocab, scale);
     return cuda_status("embedding");
+  });
+  return 0;
+}
+
+// ids [T]; table [vocab, h]; bigram [buckets + 1, h] or null; pos_table [max_pos, h] or null (with positions [T]);
+// cu [B + 1], slots [B], fresh [B]; last [state slots] int32, read and then brought up to date; out [T, h] f32.
+DINFER_API int dinfer_embedding_bigram(const int* ids, const int* prev, int prev_rows, const void* table,
+                                       const void* bigram, const void* pos_table, const int* positions, const int* cu,
+                                       const int* slots, const int* fresh, int* last, int B, float* out, int T, int h,
+                                       int vocab, int buckets, int mul_prev, int mul_cur, int max_pos, int table_dtype,
+                                       cudaStream_t stream) {
+  if (T < 0 || h <= 0 || vocab <= 0 || B <= 0) return refuse(DINFER_BAD_ARGUMENT, "embedding_bigram: bad sizes T=%d h=%d vocab=%d B=%d", T, h, vocab, B);
+  if (bigram && (buckets <= 0 || mul_prev < 0 || mul_cur < 0 || !cu || !slots || !fresh || !last))
+    return refuse(DINFER_BAD_ARGUMENT, "embedding_bigram: the bigram table needs buckets, multipliers and the requests' state");
+  if (pos_table && (!positions || max_pos <= 0)) return refuse(DINFER_BAD_ARGUMENT, "embedding_bigram: the position table needs positions");
+  if (T == 0) return 0;
+  int threads = (h + 31) / 32 * 32;
+  if (threads > 256) threads = 256;
+  DINFER_DISPATCH_DTYPE(table_dtype, TW, {
+    launch_pdl(embedding_bigram_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, prev, prev_rows, (const TW*)table,
+               (const TW*)bigram, (const TW*)pos_table, positions, cu, slots, fresh, (const int*)last, B, out, h, vocab,
+               buckets, mul_prev, mul_cur, max_pos);
+    if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return refuse((int)e, "embedding_bigram: %s", cudaGetErrorString(e));
+    if (bigram) launch_pdl(last_token_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, ids, prev, prev_rows, cu, slots, last, B, vocab);
+    return cuda_status("embedding_bigram");
+  });
+  return 0;
+}
+
+// x [T, 2*inter] with row stride ldx; out [T, inter]; scale f32 [n_scale]; index int32 [T] or null.
+DINFER_API int dinfer_gated_act_scaled(const void* x, void* out, int T, int inter, int64_t ldx, int dtype, int pairs,
+                                       int act, const float* scale, const int* index, int n_scale, cudaStream_t stream) {
+  if (T < 0 || inter <= 0 || ldx < 2 * (int64_t)inter || act < 0 || act > 3 || !scale || n_scale < 0)
+    return refuse(DINFER_BAD_ARGUMENT, "gated_act_scaled: bad arguments T=%d inter=%d ldx=%lld act=%d", T, inter, (long long)ldx, act);
+  if (T == 0) return 0;
+  int by = (inter + 255) / 256;
+  if (by > 64) by = 64;
+  DINFER_DISPATCH_DTYPE(dtype, T_, {
+    launch_pdl(gated_act_scaled_kernel<T_>, dim3(T, by), dim3(256), 0, stream, (const T_*)x, (T_*)out, inter, ldx, pairs, act,
+               scale, index, n_scale);
+    return cuda_status("gated_act_scaled");
   });
   return 0;
 }

@@ -408,6 +408,10 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
 // (x = the projection's output, plus `bias` [(H + Hkv) D + Hkv Dv] f32 where the projection has one);
 // q and k written back in place; k and v to the token's slot of a cache [blocks, 2, Hkv, block_size, Dc], whose
 // rows are Dc = max(D, Dv) wide (k in the first D, v in the first Dv elements of a row).
+// Two more steps, each off unless asked for.  A query temperature: q of a token at position p is multiplied by
+// 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1), in 32-bit, last of all.  Mixed values: v <- (1 - lam) v +
+// lam v_first with v_first [T, Hkv * Dv] (row stride ld_first) the values another layer made of the same tokens;
+// the mixed v is what the cache gets (v in the projection's row is left as it was).
 namespace {
 
 template <typename TA, typename TW>
@@ -416,7 +420,8 @@ qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict_
                         const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, int norm, int norm_first,
                         float eps, const float* __restrict__ cos_sin, int rot, int interleaved, TA* __restrict__ cache,
                         const int* __restrict__ slots, int block_size, int H, int Hkv, int D, int Dv, int Dc,
-                        const float* __restrict__ bias) {
+                        const float* __restrict__ bias, float temp_coef, int temp_every,
+                        const TA* __restrict__ v_first, int64_t ld_first, float v_lambda) {
   __shared__ float sm[WARPS][MAX_D];
   pdl_enter();
   const int t = blockIdx.x;
@@ -456,7 +461,14 @@ qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict_
       __syncwarp();
     }
     if (norm && !norm_first) normalize();
+    if (kind == 0 && temp_coef != 0.f) {
+      const float f = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.f);
+      for (int e = lane; e < D; e += 32) xs[e] *= f;
+    }
     for (int e = lane; e < D; e += 32) x[e] = from_f32<TA>(xs[e]);
+  } else if (v_first) {
+    const TA* vf = v_first + (int64_t)t * ld_first + (int64_t)(head - H - Hkv) * Dv;
+    for (int e = lane; e < Dv; e += 32) xs[e] = (1.f - v_lambda) * xs[e] + v_lambda * to_f32<TA>(vf[e]);
   }
   if (kind != 0 && cache) {
     const int slot = slots[t];
@@ -470,11 +482,16 @@ qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict_
 
 }  // namespace
 
-DINFER_API int dinfer_qkv_post_general(void* qkv, int64_t ld, const int* positions, const void* q_weight,
-                                       const void* k_weight, int norm, int norm_first, float eps, const float* cos_sin,
-                                       int rot, int interleaved, void* cache, const int* slots, int block_size, int T,
-                                       int H, int Hkv, int D, int Dv, int Dc, const float* bias, int act_dtype,
-                                       int w_dtype, cudaStream_t stream) {
+DINFER_API int dinfer_qkv_post_mixed(void* qkv, int64_t ld, const int* positions, const void* q_weight,
+                                     const void* k_weight, int norm, int norm_first, float eps, const float* cos_sin,
+                                     int rot, int interleaved, void* cache, const int* slots, int block_size, int T,
+                                     int H, int Hkv, int D, int Dv, int Dc, const float* bias, float temp_coef,
+                                     int temp_every, const void* v_first, int64_t ld_first, float v_lambda,
+                                     int act_dtype, int w_dtype, cudaStream_t stream) {
+  if (temp_coef != 0.f && temp_every <= 0)
+    return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: the query temperature's step %d must be positive", temp_every);
+  if (v_first && ld_first < (int64_t)Hkv * Dv)
+    return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: the first values' row stride is below their width");
   if (T < 0 || H <= 0 || Hkv < 0 || D <= 0 || Dv <= 0 || Dc < D || Dc < Dv)
     return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: bad sizes T=%d H=%d Hkv=%d D=%d Dv=%d Dc=%d", T, H, Hkv, D, Dv, Dc);
   if (D > MAX_D || Dv > MAX_D) return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: head sizes %d / %d above the limit %d", D, Dv, MAX_D);
@@ -488,8 +505,18 @@ DINFER_API int dinfer_qkv_post_general(void* qkv, int64_t ld, const int* positio
     DINFER_DISPATCH_DTYPE(w_dtype, TW, {
       launch_pdl(qkv_post_general_kernel<TA, TW>, grid, dim3(WARPS * 32), 0, stream, (TA*)qkv, ld, positions,
                  (const TW*)q_weight, (const TW*)k_weight, norm, norm_first, eps, cos_sin, rot, interleaved, (TA*)cache,
-                 slots, block_size, H, Hkv, D, Dv, Dc, bias);
+                 slots, block_size, H, Hkv, D, Dv, Dc, bias, temp_coef, temp_every, (const TA*)v_first, ld_first, v_lambda);
       return cuda_status("qkv_post_general");
     }));
   return 0;
+}
+
+DINFER_API int dinfer_qkv_post_general(void* qkv, int64_t ld, const int* positions, const void* q_weight,
+                                       const void* k_weight, int norm, int norm_first, float eps, const float* cos_sin,
+                                       int rot, int interleaved, void* cache, const int* slots, int block_size, int T,
+                                       int H, int Hkv, int D, int Dv, int Dc, const float* bias, int act_dtype,
+                                       int w_dtype, cudaStream_t stream) {
+  return dinfer_qkv_post_mixed(qkv, ld, positions, q_weight, k_weight, norm, norm_first, eps, cos_sin, rot, interleaved,
+                               cache, slots, block_size, T, H, Hkv, D, Dv, Dc, bias, 0.f, 1, nullptr, 0, 0.f, act_dtype,
+                               w_dtype, stream);
 }

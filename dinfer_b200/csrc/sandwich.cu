@@ -1,5 +1,6 @@
 // The joins of a layer whose sublayers have a norm on both sides, x <- x + norm_b(f(norm_a(x))), with norms whose weight
-// is one number (a gain), and the weighted average over the results of all layers so far that may follow a layer:
+// is one number (a gain) or a 32-bit vector (w_a / w_next; then every coordinate is also multiplied by its entry),
+// and the weighted average over the results of all layers so far that may follow a layer:
 //
 //   gain_norm_join   per row, everything in 32-bit:
 //                      x_new = x_in + a / sqrt(mean(a^2) + eps) * g_a                        -> x_out (may be x_in)
@@ -21,7 +22,7 @@ gain_norm_join_kernel(const TA* __restrict__ a, int64_t lda, float g_a, const fl
                       float* __restrict__ x_out, float eps, const float* __restrict__ first,
                       const float* __restrict__ results, int64_t result_stride, int n_results,
                       const TW* __restrict__ w, float* __restrict__ avg_out, float g_next, TO* __restrict__ next_out,
-                      int h) {
+                      int h, const float* __restrict__ w_a, const float* __restrict__ w_next) {
   extern __shared__ float row[];            // [h]
   __shared__ float red[33];
   pdl_enter();
@@ -34,7 +35,7 @@ gain_norm_join_kernel(const TA* __restrict__ a, int64_t lda, float g_a, const fl
   float* xo = x_out + t * h;
   ss = 0.f;
   for (int i = threadIdx.x; i < h; i += blockDim.x) {
-    float v = xr[i] + row[i] * f;
+    float v = xr[i] + row[i] * f * (w_a ? w_a[i] : 1.f);
     xo[i] = v;
     if (avg_out) {
       float y = to_f32<TW>(w[0]) * first[t * h + i];
@@ -48,7 +49,7 @@ gain_norm_join_kernel(const TA* __restrict__ a, int64_t lda, float g_a, const fl
   if (!next_out) return;
   const float fn = rsqrtf(block_sum(ss, red) / (float)h + eps) * g_next;
   TO* no = next_out + t * h;
-  for (int i = threadIdx.x; i < h; i += blockDim.x) no[i] = from_f32<TO>(row[i] * fn);
+  for (int i = threadIdx.x; i < h; i += blockDim.x) no[i] = from_f32<TO>(row[i] * fn * (w_next ? w_next[i] : 1.f));
 }
 
 template <typename T> __device__ __forceinline__ float4 load4(const T* p);
@@ -74,7 +75,7 @@ gain_norm_join_vec_kernel(const TA* __restrict__ a, int64_t lda, float g_a, cons
                           float* __restrict__ x_out, float eps, const float* __restrict__ first,
                           const float* __restrict__ results, int64_t result_stride, int n_results,
                           const TW* __restrict__ w, float* __restrict__ avg_out, float g_next, TO* __restrict__ next_out,
-                          int h) {
+                          int h, const float* __restrict__ w_a, const float* __restrict__ w_next) {
   extern __shared__ __align__(16) float row[];            // [h]
   __shared__ float red[33];
   pdl_enter();
@@ -94,7 +95,8 @@ gain_norm_join_vec_kernel(const TA* __restrict__ a, int64_t lda, float g_a, cons
   ss = 0.f;
   for (int i = threadIdx.x * 4; i < h; i += step) {
     const float4 x = load4<float>(xr + i), r = *reinterpret_cast<const float4*>(row + i);
-    float4 v = make_float4(x.x + r.x * f, x.y + r.y * f, x.z + r.z * f, x.w + r.w * f);
+    const float4 wa = w_a ? load4<float>(w_a + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+    float4 v = make_float4(x.x + r.x * f * wa.x, x.y + r.y * f * wa.y, x.z + r.z * f * wa.z, x.w + r.w * f * wa.w);
     store4<float>(xo + i, v);
     if (avg_out) {
       const float4 p = load4<float>(first + t * h + i);
@@ -115,7 +117,8 @@ gain_norm_join_vec_kernel(const TA* __restrict__ a, int64_t lda, float g_a, cons
   TO* no = next_out + t * h;
   for (int i = threadIdx.x * 4; i < h; i += step) {
     const float4 r = *reinterpret_cast<const float4*>(row + i);
-    store4<TO>(no + i, make_float4(r.x * fn, r.y * fn, r.z * fn, r.w * fn));
+    const float4 wn = w_next ? load4<float>(w_next + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+    store4<TO>(no + i, make_float4(r.x * fn * wn.x, r.y * fn * wn.y, r.z * fn * wn.z, r.w * fn * wn.w));
   }
 }
 
@@ -126,10 +129,26 @@ DINFER_DEFINE_LAST_ERROR()
 // a [T, h] rows of stride lda (a_dtype); x_in, x_out f32 [T, h] contiguous (may be the same); first f32 [T, h] and results
 // f32 rows as above with n_results - 1 earlier results (used when avg_out is given; w [n_results + 1] of w_dtype);
 // avg_out f32 [T, h] or null (it may be none of the inputs); next_out [T, h] of out_dtype or null.
+DINFER_API int dinfer_weight_norm_join(const void* a, int64_t lda, float g_a, const float* w_a, const float* x_in,
+                                       float* x_out, float eps, const float* first, const float* results,
+                                       int64_t result_stride, int n_results, const void* w, float* avg_out, float g_next,
+                                       const float* w_next, void* next_out, int T, int h, int a_dtype, int out_dtype,
+                                       int w_dtype, cudaStream_t stream);
+
 DINFER_API int dinfer_gain_norm_join(const void* a, int64_t lda, float g_a, const float* x_in, float* x_out, float eps,
                                      const float* first, const float* results, int64_t result_stride, int n_results,
                                      const void* w, float* avg_out, float g_next, void* next_out, int T, int h,
                                      int a_dtype, int out_dtype, int w_dtype, cudaStream_t stream) {
+  return dinfer_weight_norm_join(a, lda, g_a, nullptr, x_in, x_out, eps, first, results, result_stride, n_results, w,
+                                 avg_out, g_next, nullptr, next_out, T, h, a_dtype, out_dtype, w_dtype, stream);
+}
+
+// The same with per-coordinate weights of the two norms: w_a, w_next f32 [h] or null (then only the gains apply).
+DINFER_API int dinfer_weight_norm_join(const void* a, int64_t lda, float g_a, const float* w_a, const float* x_in,
+                                       float* x_out, float eps, const float* first, const float* results,
+                                       int64_t result_stride, int n_results, const void* w, float* avg_out, float g_next,
+                                       const float* w_next, void* next_out, int T, int h, int a_dtype, int out_dtype,
+                                       int w_dtype, cudaStream_t stream) {
   if (T < 0 || h <= 0 || lda < h || h > 50 * 1024)
     return refuse(DINFER_BAD_ARGUMENT, "gain_norm_join: bad sizes T=%d h=%d", T, h);
   if (avg_out && (!first || !w || n_results < 1 || (n_results > 1 && !results) || avg_out == x_out))
@@ -141,7 +160,8 @@ DINFER_API int dinfer_gain_norm_join(const void* a, int64_t lda, float g_a, cons
       DINFER_DISPATCH_DTYPE(w_dtype, TW, {
         const bool vec = h % 4 == 0 && lda % 4 == 0 && result_stride % 4 == 0 && (uintptr_t)a % 16 == 0 &&
                          (uintptr_t)x_in % 16 == 0 && (uintptr_t)x_out % 16 == 0 && (uintptr_t)first % 16 == 0 &&
-                         (uintptr_t)results % 16 == 0 && (uintptr_t)avg_out % 16 == 0 && (uintptr_t)next_out % 16 == 0;
+                         (uintptr_t)results % 16 == 0 && (uintptr_t)avg_out % 16 == 0 && (uintptr_t)next_out % 16 == 0 &&
+                         (uintptr_t)w_a % 16 == 0 && (uintptr_t)w_next % 16 == 0;
         auto k = vec ? gain_norm_join_vec_kernel<TA, TO, TW> : gain_norm_join_kernel<TA, TO, TW>;
         // few rows: the whole row at once; many rows: smaller CTAs, so that several rows' phases overlap on an SM
         const int threads = vec ? min(T >= 512 ? 256 : 1024, ((h / 4 + 31) / 32) * 32) : 256;
@@ -150,7 +170,7 @@ DINFER_API int dinfer_gain_norm_join(const void* a, int64_t lda, float g_a, cons
           if (e != cudaSuccess) return refuse((int)e, "gain_norm_join: shared memory opt-in failed: %s", cudaGetErrorString(e));
         }
         launch_pdl(k, dim3(T), dim3(threads), smem, stream, (const TA*)a, lda, g_a, x_in, x_out, eps, first, results,
-                   result_stride, n_results, (const TW*)w, avg_out, g_next, (TO*)next_out, h);
+                   result_stride, n_results, (const TW*)w, avg_out, g_next, (TO*)next_out, h, w_a, w_next);
         return cuda_status("gain_norm_join");
       })));
   return 0;

@@ -209,7 +209,8 @@ class ModelRunner:
         self.num_blocks = int(num_blocks)
         group_blocks = [max(1, self.num_blocks * bs // b) for b in sizes]
         prefix = bool(e.enable_prefix_caching)
-        if prefix and (any(g.window is not None for g in groups) or any(st is not None for st in states)):
+        if prefix and (any(g.window is not None for g in groups) or any(st is not None for st in states)
+                       or self.model.embedding_state_need() is not None):
             raise ValueError("enable_prefix_caching: this model has windowed layers or per-request state, "
                              "whose cache cannot be shared between requests")
         if e.native_host:
@@ -233,6 +234,10 @@ class ModelRunner:
                 # one slot more than requests: the rows that pad a captured batch point at it
                 binding.state = torch.zeros((e.max_num_seqs + 1,) + tuple(sn.shape), dtype=sn.dtype, device=self.device)
             self.bindings.append(binding)
+        need = self.model.embedding_state_need()
+        if need is not None:                                 # e.g. the token before, for an embedding that hashes bigrams
+            self.model.embedding_state = torch.zeros((e.max_num_seqs + 1,) + tuple(need.shape), dtype=need.dtype,
+                                                     device=self.device)
 
     # ---- one step
     def step(self, entries: Sequence[StepEntry], placeholders: bool = False) -> torch.Tensor:

@@ -216,11 +216,14 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_
                  cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
                  head_dim: int, scale: float, window: int, max_q_len: int, any_decode: bool,
                  any_prefill: bool, splits: int, scratch: Optional[torch.Tensor] = None,
-                 sink: bool = False) -> torch.Tensor:
+                 sink: bool = False, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged causal attention on the tensor cores.  ``q`` / ``out``: rows with a contiguous last axis,
     head h at columns [h*D, (h+1)*D).  ``splits`` > 1 needs ``scratch`` (f32) of
-    ``B * H * splits * (D + 2)`` elements; it is allocated here when not given."""
-    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
+    ``B * H * splits * (D + 2)`` elements; it is allocated here when not given.  ``slopes`` (f32 [H]): a distance
+    bias, ``score_ij - slopes[h] * (i - j)``."""
+    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens, slopes)
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != num_heads or not slopes.is_contiguous()):
+        raise KernelError("attention_tc: slopes float32 [H]")
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: bfloat16 only")
     if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
@@ -237,12 +240,14 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_
         scratch = torch.empty(B * num_heads * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
     if splits > 1 and (scratch.dtype != torch.float32 or scratch.numel() < B * num_heads * splits * (head_dim + 2)):
         raise KernelError("attention_tc: scratch too small")
-    lib, f = _fn("attention_tc", "dinfer_attention_tc_sink",
+    lib, f = _fn("attention_tc", "dinfer_attention_tc_bias",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                  c_void_p])
     check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), ptr(block_table), block_table.shape[1],
                  ptr(cu_seqlens), ptr(seq_lens), B, num_heads, num_kv_heads, head_dim, cache.shape[3],
-                 float(scale), int(window), int(bool(sink)), int(max_q_len), int(any_decode), int(any_prefill), int(splits),
+                 float(scale), int(window), int(bool(sink)), ptr(slopes), int(max_q_len), int(any_decode), int(any_prefill),
+                 int(splits),
                  ptr(scratch if splits > 1 else None), stream_handle()), "attention_tc")
     return out
 

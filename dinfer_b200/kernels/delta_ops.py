@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from ctypes import c_float, c_int, c_int64, c_void_p
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -88,20 +88,26 @@ def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     return out
 
 
-def post(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, sigmoid_gate: bool,
+def post(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], eps: float, sigmoid_gate: bool,
          out: torch.Tensor) -> torch.Tensor:
     """``out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h])`` with act = sigmoid or silu; o f32 [T, H, dv],
-    gate [T, H * dv] (its own dtype) and out [T, H * dv] of the activations' dtype (views with a row stride are fine)."""
+    gate [T, H * dv] (its own dtype; None: no gate) and out [T, H * dv] of the activations' dtype (views with a row
+    stride are fine).  ``weight`` f32 [dv] (one row for all heads) or [H * dv] (every head its own)."""
     require_cuda(o, weight, gate, out)
     T, H, dv = o.shape
-    _rows_contiguous(gate, "delta post gate")
+    if gate is not None:
+        _rows_contiguous(gate, "delta post gate")
     _rows_contiguous(out, "delta post out")
-    if o.dtype != torch.float32 or not o.is_contiguous() or weight.dtype != torch.float32 or weight.numel() != dv \
-            or gate.shape[0] != T or gate.shape[1] < H * dv or tuple(out.shape) != (T, H * dv):
-        raise KernelError("delta post: o f32 [T, H, dv], weight f32 [dv], gate / out [T, H * dv]")
-    lib, f = _fn("delta_rule", "dinfer_delta_post",
+    if o.dtype != torch.float32 or not o.is_contiguous() or weight.dtype != torch.float32 \
+            or weight.numel() not in (dv, H * dv) or not weight.is_contiguous() \
+            or (gate is not None and (gate.shape[0] != T or gate.shape[1] < H * dv)) or tuple(out.shape) != (T, H * dv):
+        raise KernelError("delta post: o f32 [T, H, dv], weight f32 [dv] or [H * dv], gate / out [T, H * dv]")
+    per_head = weight.numel() == H * dv and H > 1
+    lib, f = _fn("delta_rule", "dinfer_delta_post_ex",
                  [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_int,
-                  c_int, c_void_p])
-    check(lib, f(ptr(o), ptr(weight), ptr(gate), gate.stride(0), ptr(out), out.stride(0), T, H, dv, float(eps),
-                 int(bool(sigmoid_gate)), dtype_code(gate.dtype), dtype_code(out.dtype), stream_handle()), "delta_post")
+                  c_int, c_int, c_void_p])
+    check(lib, f(ptr(o), ptr(weight), ptr(gate), gate.stride(0) if gate is not None else 0, ptr(out), out.stride(0), T, H,
+                 dv, float(eps), int(bool(sigmoid_gate)), int(per_head),
+                 dtype_code(gate.dtype if gate is not None else torch.float32), dtype_code(out.dtype), stream_handle()),
+          "delta_post")
     return out

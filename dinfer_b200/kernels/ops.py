@@ -51,6 +51,45 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
     return out
 
 
+def embedding_bigram(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, bigram: Optional[torch.Tensor],
+                     hashing, pos_table: Optional[torch.Tensor], positions: torch.Tensor, cu_seqlens: torch.Tensor,
+                     slots: torch.Tensor, fresh: torch.Tensor, last: Optional[torch.Tensor],
+                     prev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[id] + bigram[(before * mul_prev + id * mul_cur) mod buckets] + pos_table[positions[t]]`` into the
+    f32 residual stream; ``hashing`` = (buckets, mul_prev, mul_cur); ``before`` is the token before in the same request
+    (row ``buckets`` of the bigram table for a request's first token).  The token before a step's first one comes from
+    ``last[slots[b]]`` (int32, one per state slot; not read for a fresh request), which then takes the request's last
+    token of this step.  ``bigram`` / ``pos_table`` None: that term is left out.  ``prev``: as in ``embedding``."""
+    require_cuda(ids, table, out, bigram, pos_table, positions, cu_seqlens, slots, fresh, last, prev)
+    T, h = out.shape
+    if ids.dtype != torch.int32 or out.dtype != torch.float32 or not out.is_contiguous() \
+            or not table.is_contiguous() or table.shape[1] != h or ids.numel() != T:
+        raise KernelError("embedding_bigram: ids int32 [T], table [V, h] contiguous, out f32 [T, h] contiguous")
+    buckets, mul_prev, mul_cur = (int(v) for v in hashing) if bigram is not None else (0, 0, 0)
+    if bigram is not None:
+        if bigram.dtype != table.dtype or not bigram.is_contiguous() or tuple(bigram.shape) != (buckets + 1, h):
+            raise KernelError("embedding_bigram: the bigram table is [buckets + 1, h] of the table's dtype")
+        if last is None or last.dtype != torch.int32 or not last.is_contiguous():
+            raise KernelError("embedding_bigram: last int32 [state slots]")
+    if pos_table is not None and (pos_table.dtype != table.dtype or not pos_table.is_contiguous() or pos_table.shape[1] != h):
+        raise KernelError("embedding_bigram: the position table is [positions, h] of the table's dtype")
+    for t in (positions, cu_seqlens, slots, fresh) + ((prev,) if prev is not None else ()):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("embedding_bigram: positions, offsets, slots, fresh flags and prev are contiguous int32")
+    B = cu_seqlens.numel() - 1
+    lib, f = _fn("elementwise", "dinfer_embedding_bigram",
+                 [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(ids), ptr(prev), prev.numel() if prev is not None else 0, ptr(table), ptr(bigram), ptr(pos_table),
+                 ptr(positions), ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(last), B, ptr(out), T, h, table.shape[0],
+                 buckets, mul_prev, mul_cur, pos_table.shape[0] if pos_table is not None else 0, dtype_code(table.dtype),
+                 stream_handle()), "embedding_bigram")
+    if bigram is not None and T > 0:
+        from .lib import add_launches
+        add_launches(1)                                   # the kernel that stores the requests' last tokens
+    return out
+
+
 def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     """x = cap * tanh(x / cap) in place (float32, contiguous): logits with a soft cap."""
     require_cuda(x)
@@ -223,12 +262,15 @@ def qk_post(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_h
 def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
                       head_dim: int, scale: float, window: int = 0, v_dim: Optional[int] = None,
-                      sink: bool = False) -> torch.Tensor:
+                      sink: bool = False, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged causal attention, plain arithmetic, any head size.  ``q`` may be a strided view (for
     instance the q columns of the qkv rows).  ``v_dim``: the values' width where it differs from the keys' (the
     cache's rows are then ``max(head_dim, v_dim)`` wide, ``out`` holds head h at ``h * v_dim``); ``sink``: one more
-    term of score 0 and no value in the softmax's denominator."""
-    require_cuda(q, out, cache, block_table, cu_seqlens, positions)
+    term of score 0 and no value in the softmax's denominator; ``slopes`` (f32 [H]): a distance bias,
+    ``score_ij - slopes[h] * (i - j)``."""
+    require_cuda(q, out, cache, block_table, cu_seqlens, positions, slopes)
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != num_heads or not slopes.is_contiguous()):
+        raise KernelError("attention: slopes float32 [H]")
     _rows_contiguous(q, "attention q")
     _rows_contiguous(out, "attention out")
     T = q.shape[0]
@@ -245,12 +287,12 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != row \
             or not cache.is_contiguous():
         raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, {row}]")
-    lib, f = _fn("attention_generic", "dinfer_attention_generic_ex",
+    lib, f = _fn("attention_generic", "dinfer_attention_generic_bias",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p])
     check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), ptr(block_table),
                  block_table.shape[1], ptr(cu_seqlens), ptr(positions), T, B, num_heads, num_kv_heads,
-                 head_dim, v_dim, row, cache.shape[3], float(scale), int(window), int(bool(sink)),
+                 head_dim, v_dim, row, cache.shape[3], float(scale), int(window), int(bool(sink)), ptr(slopes),
                  dtype_code(q.dtype), stream_handle()), "attention_generic")
     return out
 
@@ -259,12 +301,19 @@ def qkv_post_general(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int,
                      v_dim: int, eps: float, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
                      norm: bool, norm_first: bool, cos_sin: Optional[torch.Tensor], cache: Optional[torch.Tensor],
                      slots: Optional[torch.Tensor], block_size: int, interleaved: bool = False,
-                     bias: Optional[torch.Tensor] = None) -> None:
+                     bias: Optional[torch.Tensor] = None, q_temperature=None, v_first: Optional[torch.Tensor] = None,
+                     v_lambda: float = 0.0) -> None:
     """The general q/k/v post-processing: per-head RMS norm of q and k (``norm``; the weights may be None: a norm
     without a weight) before or behind (``norm_first``) the rotation, q and k written back in place, k and v (v of
     width ``v_dim``) into a paged cache whose rows are ``max(head_dim, v_dim)`` wide.  ``bias``: f32, one per column of
-    the q, k, v projections, added first (a projection whose bias has no kernel of its own)."""
-    require_cuda(qkv, positions, q_weight, k_weight, cos_sin, cache, slots, bias)
+    the q, k, v projections, added first (a projection whose bias has no kernel of its own).  ``q_temperature`` =
+    (coef, every): q at position p times ``1 + coef * ln(floor((p + 1) / every) + 1)``.  ``v_first`` [T, Hkv * v_dim]
+    (rows with a stride are fine) and ``v_lambda``: the cache gets ``(1 - v_lambda) v + v_lambda v_first``."""
+    require_cuda(qkv, positions, q_weight, k_weight, cos_sin, cache, slots, bias, v_first)
+    coef, every = (float(q_temperature[0]), int(q_temperature[1])) if q_temperature else (0.0, 1)
+    if v_first is not None and (v_first.dtype != qkv.dtype or v_first.stride(1) != 1 or v_first.shape[0] != qkv.shape[0]
+                                or v_first.shape[1] != num_kv_heads * v_dim):
+        raise KernelError("qkv_post_general: v_first [T, Hkv * v_dim] of the activations' dtype")
     if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous()
                              or bias.numel() != (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_dim):
         raise KernelError("qkv_post_general: bias f32 [(H + Hkv) * D + Hkv * Dv]")
@@ -288,12 +337,14 @@ def qkv_post_general(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int,
                 or slots.numel() != T or tuple(cache.shape[1:]) != (2, num_kv_heads, block_size, row):
             raise KernelError(f"qkv_post_general: cache [blocks, 2, {num_kv_heads}, {block_size}, {row}] of the "
                               f"activations' dtype, contiguous; slots int32 [T]")
-    lib, f = _fn("qk_post", "dinfer_qkv_post_general",
+    lib, f = _fn("qk_post", "dinfer_qkv_post_mixed",
                  [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
-                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int, c_void_p,
+                  c_int64, c_float, c_int, c_int, c_void_p])
     check(lib, f(ptr(qkv), qkv.stride(0), ptr(positions), ptr(q_weight), ptr(k_weight), int(bool(norm)),
                  int(bool(norm_first)), float(eps), ptr(cos_sin), rot, int(bool(interleaved)), ptr(cache), ptr(slots),
-                 block_size, T, num_heads, num_kv_heads, head_dim, v_dim, row, ptr(bias), dtype_code(qkv.dtype), dtype_code(w_dt),
+                 block_size, T, num_heads, num_kv_heads, head_dim, v_dim, row, ptr(bias), coef, every, ptr(v_first),
+                 v_first.stride(0) if v_first is not None else 0, float(v_lambda), dtype_code(qkv.dtype), dtype_code(w_dt),
                  stream_handle()), "qkv_post_general")
 
 
@@ -415,6 +466,28 @@ def gated_act(x: torch.Tensor, out: torch.Tensor, activation: str = "silu", pair
     lib, f = _fn("elementwise", "dinfer_gated_act", [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p])
     check(lib, f(ptr(x), ptr(out), T, inter, x.stride(0), dtype_code(x.dtype), int(bool(pairs)),
                  GATE_ACTIVATIONS[activation], stream_handle()), "gated_act")
+    return out
+
+
+def gated_act_scaled(x: torch.Tensor, out: torch.Tensor, scale: torch.Tensor, index: Optional[torch.Tensor] = None,
+                     activation: str = "silu", pairs: bool = False) -> torch.Tensor:
+    """``out[t, i] = act(s_t gate_i) * (s_t up_i)`` with ``s_t = scale[index[t]]`` (``scale[t]`` without an index; a row
+    whose index is outside ``scale`` gives zeros); layouts and activations of ``gated_act``."""
+    require_cuda(x, out, scale, index)
+    _rows_contiguous(x, "gated_act_scaled")
+    T, two_i = x.shape
+    inter = two_i // 2
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"gated_act_scaled: unknown activation {activation!r}")
+    if two_i % 2 or out.shape != (T, inter) or not out.is_contiguous() or out.dtype != x.dtype:
+        raise KernelError("gated_act_scaled: x [T, 2I], out [T, I] contiguous, same dtype")
+    if scale.dtype != torch.float32 or not scale.is_contiguous() or (index is None and scale.numel() < T) \
+            or (index is not None and (index.dtype != torch.int32 or index.numel() != T or not index.is_contiguous())):
+        raise KernelError("gated_act_scaled: scale f32 contiguous, index int32 [T]")
+    lib, f = _fn("elementwise", "dinfer_gated_act_scaled",
+                 [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    check(lib, f(ptr(x), ptr(out), T, inter, x.stride(0), dtype_code(x.dtype), int(bool(pairs)),
+                 GATE_ACTIVATIONS[activation], ptr(scale), ptr(index), scale.numel(), stream_handle()), "gated_act_scaled")
     return out
 
 

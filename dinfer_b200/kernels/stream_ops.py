@@ -12,15 +12,26 @@ from .lib import KernelError, check, dtype_code, ptr, require_cuda, stream_handl
 from .ops import _fn, _rows_contiguous
 
 
-def gain_norm_join(a: torch.Tensor, gain: float, eps: float, x_in: torch.Tensor, x_out: torch.Tensor,
-                   average=None, next_gain: Optional[float] = None, next_out: Optional[torch.Tensor] = None) -> None:
-    """``x_out = x_in + a / rms(a) * gain`` (32-bit rows [T, h]; ``x_out`` may be ``x_in``).  ``average`` =
+def gain_norm_join(a: torch.Tensor, gain, eps: float, x_in: torch.Tensor, x_out: torch.Tensor,
+                   average=None, next_gain=None, next_out: Optional[torch.Tensor] = None) -> None:
+    """``x_out = x_in + a / rms(a) * gain`` (32-bit rows [T, h]; ``x_out`` may be ``x_in``).  ``gain`` and ``next_gain``
+    are each one number or a float32 vector [h] of per-coordinate weights.  ``average`` =
     (first [T, h], results [count, T, h], n, weights [n + 1], out [T, h]): ``out = weights[0] * first + sum_(j=1..n-1)
     weights[j] * results[j - 1] + weights[n] * x_out``.  ``next_out`` (the activations' dtype): the RMS norm with
     ``next_gain`` of the average, or of ``x_out`` without one."""
     require_cuda(a, x_in, x_out, next_out)
     _rows_contiguous(a, "gain_norm_join")
     T, h = x_in.shape
+
+    def split(g):                                          # (the number, the vector) of a norm's weight
+        if isinstance(g, torch.Tensor):
+            require_cuda(g)
+            if g.dtype != torch.float32 or g.numel() != h or not g.is_contiguous():
+                raise KernelError("gain_norm_join: a norm's weight vector is contiguous float32 [h]")
+            return 1.0, g
+        return float(g or 0.0), None
+    g_a, w_a = split(gain)
+    g_n, w_n = split(next_gain)
     for t in (x_in, x_out):
         if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != (T, h):
             raise KernelError("gain_norm_join: the stream is contiguous float32 [T, h]")
@@ -42,11 +53,11 @@ def gain_norm_join(a: torch.Tensor, gain: float, eps: float, x_in: torch.Tensor,
             stride = results.stride(0)
     if next_out is not None and (tuple(next_out.shape) != (T, h) or not next_out.is_contiguous() or next_gain is None):
         raise KernelError("gain_norm_join: next_out contiguous [T, h] with its gain")
-    lib, f = _fn("sandwich", "dinfer_gain_norm_join",
-                 [c_void_p, c_int64, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_void_p,
-                  c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    check(lib, f(ptr(a), a.stride(0), float(gain), ptr(x_in), ptr(x_out), float(eps), ptr(first), ptr(results), stride,
-                 int(n), ptr(weights), ptr(out), float(next_gain or 0.0), ptr(next_out), T, h, dtype_code(a.dtype),
+    lib, f = _fn("sandwich", "dinfer_weight_norm_join",
+                 [c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int,
+                  c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(a), a.stride(0), g_a, ptr(w_a), ptr(x_in), ptr(x_out), float(eps), ptr(first), ptr(results), stride,
+                 int(n), ptr(weights), ptr(out), g_n, ptr(w_n), ptr(next_out), T, h, dtype_code(a.dtype),
                  dtype_code(next_out.dtype if next_out is not None else torch.float32),
                  dtype_code(weights.dtype if weights is not None else torch.float32), stream_handle()), "gain_norm_join")
 

@@ -11,12 +11,12 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from ..parts import (attention, block, delta_rule, differential_attention, latent_attention, mlp, moe,  # noqa: F401
-                     norm, parallel_mixers, retention, rope, short_conv)   # (register the built-in parts)
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheBinding, ResidualStream,
+from ..parts import (attention, block, delta_rule, differential_attention, embedding, latent_attention,  # noqa: F401
+                     linear_state, mlp, moe, norm, parallel_mixers, retention, rope, short_conv)   # (register the built-in parts)
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheBinding, ResidualStream,
                           StepContext, build_part)
 from ..parts.linear import Linear
-from ..parts.spec import ModelSpec, TensorDecl
+from ..parts.spec import ModelSpec, PartSpec, TensorDecl
 
 
 class DecoderModel:
@@ -35,13 +35,17 @@ class DecoderModel:
             blk.configure(ls.extras, env, ls.prefix)
             self.blocks.append(blk)
         self.final_norm = build_part(NORMS, spec.final_norm, env, "")
+        emb = spec.embedding or PartSpec("table", {"tensor": spec.embedding_tensor, "vocab_size": spec.vocab_size,
+                                                   "scale": spec.embedding_scale})
+        self.embed = build_part(EMBEDDINGS, emb, env, "")
         self.embedding: Optional[torch.Tensor] = None
+        self.embedding_state: Optional[torch.Tensor] = None     # what the embedding keeps per request (the runner makes it)
         self.lm_head: Optional[Linear] = None
 
     # ---- weights
     def declarations(self) -> List[TensorDecl]:
         s = self.spec
-        d = [TensorDecl(s.embedding_tensor, (s.vocab_size, s.hidden_size))]
+        d = self.embed.declare()
         for b in self.blocks:
             for p in b.parts():
                 d += p.declare()
@@ -54,7 +58,8 @@ class DecoderModel:
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        self.embedding = tensors[s.embedding_tensor].contiguous()
+        self.embed.bind(tensors)
+        self.embedding = self.embed.table
         for b in self.blocks:
             for p in b.parts():
                 p.bind(tensors)
@@ -62,6 +67,10 @@ class DecoderModel:
         self.final_norm.bind(tensors)
         head = tensors.get(s.lm_head_tensor)
         self.lm_head = Linear(head if head is not None else self.embedding)
+
+    def embedding_state_need(self):
+        """What the embedding keeps per request (a ``StateNeed``), or None."""
+        return self.embed.state_need()
 
     def kernel_libraries(self) -> List[str]:
         libs = ["elementwise"] + self.lm_head.kernel_libraries() + self.final_norm.kernel_libraries()
@@ -101,9 +110,7 @@ class DecoderModel:
                 logits_rows: torch.Tensor) -> torch.Tensor:
         """ids [T] int32 -> logits [R, V] float32 at the rows ``logits_rows`` [R] int32."""
         s = self.spec
-        T = ids.numel()
-        x = torch.empty((T, s.hidden_size), dtype=torch.float32, device=ids.device)
-        ops.embedding(ids, self.embedding, x, prev=ctx.prev_tokens, scale=s.embedding_scale)
+        x = self.embed.forward(ids, ctx, self.embedding_state)
         ctx.token_ids = ids
         stream = ResidualStream(x)
         order = [self.blocks[e.layer] for e in s.schedule]

@@ -31,7 +31,13 @@ class GQAttention(Mixer):
     ``v_dim`` (the values' width where it differs from ``head_dim``), ``qk_norm_order`` ("before" the rotation, the
     default, or "after" it), ``qk_norm_weight`` (False: the head norm has no weight), ``sink`` (the softmax has one
     more term of score 0 that carries no value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``), ``out_float32`` (the output
-    projection's result stays 32-bit, for an arrangement that norms it before it joins the stream)."""
+    projection's result stays 32-bit, for an arrangement that norms it before it joins the stream).
+    ``q_temperature`` = (coef, every): q at position p is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``.
+    ``distance_slopes``: a distance bias ``- slope_h * (i - j)`` on the scores; "geometric" (``slope_h = 2^(-8 (h + 1) /
+    H)``) or one number per head.  ``value_mix`` = {"weight": tensor name of one number lambda, "key": any name}: the
+    first layer of a model with this key keeps its values of the step's tokens, every later one caches
+    ``(1 - lambda) v + lambda v_first`` instead of its own v (the first one's tensor is not used).  ``gate_proj``: the
+    heads are multiplied by ``sigmoid(W_g x)`` before the output projection."""
 
     def __init__(self, params, env: BuildEnv, prefix=""):
         super().__init__(params, env, prefix)
@@ -56,8 +62,20 @@ class GQAttention(Mixer):
         self.norm_weight = bool(p.get("qk_norm_weight", True))
         if p.get("qk_norm_order", "before") not in ("before", "after") or self.Dv <= 0:
             raise ValueError("attention: qk_norm_order is before or after, v_dim positive")
+        self.q_temperature = tuple(p["q_temperature"]) if p.get("q_temperature") else None
+        if self.q_temperature and (float(self.q_temperature[0]) == 0.0):
+            self.q_temperature = None
+        slopes = p.get("distance_slopes")
+        if slopes == "geometric":
+            slopes = [2.0 ** (-8.0 * (h + 1) / self.H) for h in range(self.H)]
+        if slopes is not None and len(slopes) != self.H:
+            raise ValueError("attention: distance_slopes is 'geometric' or one number per head")
+        self.slope_values = [float(v) for v in slopes] if slopes is not None else None
+        self.value_mix = dict(p["value_mix"]) if p.get("value_mix") else None
+        self.gate_name = prefix + p["gate_proj"] if p.get("gate_proj") else None
         # the q/k kernel with lane paths takes the usual order and equal widths; anything else takes the general one
-        self.general = self.Dv != self.D or (self.qk_norm and (self.norm_after or not self.norm_weight))
+        self.general = (self.Dv != self.D or (self.qk_norm and (self.norm_after or not self.norm_weight))
+                        or self.q_temperature is not None or self.value_mix is not None)
         pos: PartSpec = p.get("position") or PartSpec("none")
         self.position = build_part(POSITION_ENCODINGS, pos, env, prefix)
         n = lambda key, default: prefix + p.get(key, default)
@@ -66,6 +84,10 @@ class GQAttention(Mixer):
             "v": n("v_proj", "v_proj.weight"), "o": n("o_proj", "o_proj.weight"),
             "qn": n("q_norm", "q_norm.weight"), "kn": n("k_norm", "k_norm.weight"),
         }
+        if self.value_mix:
+            self.names["vmix"] = prefix + self.value_mix["weight"]
+        self.slopes = None
+        self.v_lambda = 0.0
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
         self.q_norm_w = self.k_norm_w = None
@@ -78,6 +100,10 @@ class GQAttention(Mixer):
             d += [TensorDecl(self.names["qn"], (D,), init="ones"), TensorDecl(self.names["kn"], (D,), init="ones")]
         if self.bias:
             d += [TensorDecl(self._bias_name(x), (n,)) for x, n in (("q", H * D), ("k", Hkv * D), ("v", Hkv * Dv), ("o", h))]
+        if self.value_mix:
+            d.append(TensorDecl(self.names["vmix"], ()))
+        if self.gate_name:
+            d.append(TensorDecl(self.gate_name, (H * Dv, h)))
         return d
 
     def _bias_name(self, which: str) -> str:
@@ -96,7 +122,21 @@ class GQAttention(Mixer):
             o_bias = tensors[self._bias_name("o")]
         # with the general q/k/v kernel the projection's bias is added there, not by a kernel of its own
         self.qkv_bias32 = qkv_bias.float().contiguous() if (self.general and qkv_bias is not None) else None
-        self.qkv = Linear(torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0), None if self.general else qkv_bias)
+        rows = [q.to(dt), k.to(dt), v.to(dt)]
+        self.gate_col = 0
+        if self.gate_name:                                   # the gate rides behind q, k, v, from a multiple of 8 columns on
+            if self.bias:
+                raise ValueError("attention: a gate beside projections with biases is not built")
+            used = sum(t.shape[0] for t in rows)
+            self.gate_col = (used + 7) // 8 * 8
+            if self.gate_col > used:
+                rows.append(q.new_zeros((self.gate_col - used, q.shape[1]), dtype=dt))
+            rows.append(tensors[self.gate_name].to(dt))
+        self.qkv = Linear(torch.cat(rows, dim=0), None if self.general else qkv_bias)
+        if self.slope_values is not None:
+            self.slopes = torch.tensor(self.slope_values, dtype=torch.float32, device=q.device)
+        if self.value_mix:
+            self.v_lambda = float(tensors[self.names["vmix"]].float().item())
         self.o = Linear(tensors[self.names["o"]], o_bias)
         if self.qk_norm and self.norm_weight:
             self.q_norm_w = tensors[self.names["qn"]].contiguous()
@@ -109,11 +149,15 @@ class GQAttention(Mixer):
         """Whether the tensor-core kernels take this attention: keys and values of one width."""
         return self.Dv == self.D and attention_ops.tc_supported(dtype, self.D, self.H // self.Hkv)
 
+    def _umma_ok(self) -> bool:
+        """The tcgen05 prompt kernels and the TMA decode kernel know no distance bias."""
+        return self.slopes is None and self.slope_values is None
+
     def kernel_libraries(self):
         att = ["attention_generic"]
         if self._fast(self.env.act_dtype):
             att = ["attention_tc"]
-            if self.D in (64, 128):
+            if self.D in (64, 128) and self._umma_ok():
                 att += ["attention_decode", "attention_umma", "attention_umma64"]
         return ["qk_post"] + att + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
@@ -133,9 +177,19 @@ class GQAttention(Mixer):
             if not self.position.fused:
                 raise NotImplementedError("attention: a head norm behind the rotation, or values of another width, "
                                           "need a position encoding the q/k kernel applies")
+            v_first = None
+            if self.value_mix:
+                # the first layer with this key leaves its values of the step's tokens for the later ones
+                key = ("value_mix", self.value_mix.get("key", ""))
+                owner, v_first = ctx.derived.get(key, (None, None))
+                if owner is None or owner is self:          # (the same context may run twice: a graph's warm-up)
+                    at = (H + Hkv) * D
+                    ctx.derived[key] = (self, qkv[:, at:at + Hkv * self.Dv])
+                    v_first = None
             ops.qkv_post_general(qkv, ctx.positions, H, Hkv, D, self.Dv, self.eps, self.q_norm_w, self.k_norm_w,
                                  self.qk_norm, not self.norm_after, table, kv, g.slot_mapping, g.block_size,
-                                 interleaved=getattr(self.position, "interleaved", False), bias=self.qkv_bias32)
+                                 interleaved=getattr(self.position, "interleaved", False), bias=self.qkv_bias32,
+                                 q_temperature=self.q_temperature, v_first=v_first, v_lambda=self.v_lambda)
         elif self.position.fused:
             ops.qk_post(qkv, ctx.positions, H, Hkv, D, self.eps, self.q_norm_w, self.k_norm_w, table,
                         kv, g.slot_mapping, g.block_size, interleaved=getattr(self.position, "interleaved", False))
@@ -151,6 +205,8 @@ class GQAttention(Mixer):
                             g.slot_mapping, g.block_size)
         out = torch.empty((qkv.shape[0], H * self.Dv), dtype=qkv.dtype, device=qkv.device)
         self.attend(qkv[:, :H * D], out, cache.kv, g, ctx)
+        if self.gate_name:
+            ops.sigmoid_gate(out, qkv[:, self.gate_col:self.gate_col + H * self.Dv])
         if sink is not None:                               # (residual, the norm behind this mixer)
             return self.o.into_residual(out, sink[0], sink[1])
         return self.o(out, out_dtype=torch.float32 if self.out_float32 else None)
@@ -163,13 +219,14 @@ class GQAttention(Mixer):
             splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, self.Hkv, ctx.max_seq_len)
             tc_decode = ctx.any_decode
             if ctx.any_decode and attention_ops.decode_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size) \
-                    and (g.block_size >= 8 or not self.sink):
+                    and (g.block_size >= 8 or not self.sink) and self._umma_ok():
                 # decoded tokens: the kernel made for them (keys on the tile's rows, in-kernel fold)
                 attention_ops.attention_decode(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                                self.Hkv, self.D, self.scale, window, splits, sink=self.sink)
                 tc_decode = False
             tc_prefill = ctx.any_prefill
-            if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
+            if ctx.any_prefill and self._umma_ok() \
+                    and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
                 # prompt portions: tcgen05 / TMEM / TMA
                 key = ("attention_umma", self.H, self.Hkv, self.D)
                 shape = ctx.derived.get(key)
@@ -193,7 +250,7 @@ class GQAttention(Mixer):
             if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                            self.Hkv, self.D, self.scale, window, ctx.max_q_len, tc_decode,
-                                           tc_prefill, splits, sink=self.sink)
+                                           tc_prefill, splits, sink=self.sink, slopes=self.slopes)
         else:
             ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
-                                  self.D, self.scale, window, v_dim=self.Dv, sink=self.sink)
+                                  self.D, self.scale, window, v_dim=self.Dv, sink=self.sink, slopes=self.slopes)

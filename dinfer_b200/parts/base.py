@@ -8,6 +8,7 @@ No part knows which model it is in.
     FeedForward     forward(x [T, h], ctx) -> [T, h]
     Norm            forward(residual f32 [T, h], delta | None, rows | None) -> normed [R, h]
     PositionEncoding  a mixer's helper; see parts/rope.py
+    Embedding       forward(ids [T], ctx, state) -> residual f32 [T, h]
     Block           forward(stream: ResidualStream, ctx, cache) -> None   (arranges the four)
 """
 from __future__ import annotations
@@ -184,6 +185,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids -> the first rows of the residual stream.  ``table`` [vocab, h] is the tensor a head that is tied to the
+    embedding multiplies by.  An embedding that keeps something per request says so in ``state_need`` and gets
+    ``state`` [max_num_seqs + 1, *shape], indexed by ``ctx.state_slots`` like a mixer's."""
+    table: Optional[torch.Tensor] = None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, ids: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """ids int32 [T] -> float32 [T, h] (a new tensor)."""
+        raise NotImplementedError
+
+
 class Norm(Part):
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -312,6 +327,7 @@ class Registry:
         return sorted(self._items)
 
 
+EMBEDDINGS = Registry("embedding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")

@@ -178,7 +178,8 @@ class PostNormResidual(Block):
 @BLOCKS.register("sandwich_residual")
 class SandwichResidual(Block):
     """``x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x)))``: every sublayer has a norm on its input and one on
-    its output, all four RMS norms whose weight is one number.  A layer may have no feed-forward (kind "none").
+    its output, all four RMS norms whose weight is one number or a vector kept in 32-bit (a norm with an ``offset``).
+    A layer may have no feed-forward (kind "none").
 
     extras: ``depth_average`` (tensor name after the layer's prefix) and ``depth_index`` (how many layers ran before
     this one): with X_0 what the embedding gave and X_(j+1) the result of layer j, what leaves layer i is
@@ -217,10 +218,15 @@ class SandwichResidual(Block):
     def _no_feed_forward(self) -> bool:
         return bool(getattr(self.feed_forward, "absent", False))
 
-    def _gain(self, norm) -> float:
-        if not isinstance(norm, RMSNorm) or norm.gain is None:
-            raise TypeError("sandwich_residual: the norms are RMS norms whose weight is one number")
-        return norm.gain
+    def _gain(self, norm):
+        """One number, or the norm's weight vector in 32-bit."""
+        if isinstance(norm, RMSNorm) and norm.gain is not None:
+            return norm.gain
+        if isinstance(norm, RMSNorm) and norm.weight is not None:
+            if norm.weight.dtype != torch.float32:
+                norm.weight = norm.weight.to(torch.float32).contiguous()
+            return norm.weight
+        raise TypeError("sandwich_residual: the norms are RMS norms with a weight")
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding,
                 next_block: Optional[Block] = None) -> None:
@@ -263,7 +269,7 @@ class SandwichResidual(Block):
         a = self.mixer.forward(hin, ctx, cache)
         last = self._no_feed_forward()
         nxt = next_block.mixer_norm if (isinstance(next_block, SandwichResidual) and next_block.mixer_norm.eps == eps
-                                        and next_block.mixer_norm.gain is not None) else None
+                                        and next_block.mixer_norm.weight is not None) else None
 
         def join(branch, norm, x_from, final: bool):
             follow = nxt if final else self.feed_forward_norm

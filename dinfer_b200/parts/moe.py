@@ -36,7 +36,9 @@ class MoE(FeedForward):
     shared expert's output times ``sigmoid(w_g . x)``; None: added as it is), and the tensor names ``router``,
     ``expert_up`` / ``expert_down`` (with ``{e}`` for the expert's index), ``shared_up``, ``shared_down``,
     ``shared_gate_proj``.  ``routing`` ("router", the default, or "table": tensor name ``table``), ``gated`` (experts
-    and the shared expert have a gate matrix: names ``expert_gate``, ``shared_gate_up``)."""
+    and the shared expert have a gate matrix: names ``expert_gate``, ``shared_gate_up``).  ``weight_on`` ("output", the
+    default: ``sum_k w_k expert_k(x)``; "input": ``sum_k expert_k(w_k x)``, gated experts only: the weight is applied
+    to the first product's result, in 32-bit, ahead of the activation)."""
 
     def __init__(self, params, env, prefix=""):
         super().__init__(params, env, prefix)
@@ -52,6 +54,10 @@ class MoE(FeedForward):
         self.routing = str(p.get("routing", "router"))
         self.gated = bool(p.get("gated", False))
         self.vocab = int(p.get("vocab_size", 0))
+        self.weight_on_input = p.get("weight_on", "output") == "input"
+        if p.get("weight_on", "output") not in ("output", "input") or (self.weight_on_input and not self.gated):
+            raise ValueError("moe: weight_on is output or input, and input needs gated experts")
+        self._ones = {}
         if self.routing not in ("router", "table") or (self.routing == "table" and (self.vocab <= 0 or self.shared_gate)):
             raise ValueError("moe: routing is router or table; a table needs vocab_size and takes no gate on the shared expert")
         if not (0 < self.top <= self.E):
@@ -150,7 +156,7 @@ class MoE(FeedForward):
             a = moe_ops.gather_rows(x, order, pairs, self.top)
             u = torch.empty((order.numel(), wide), dtype=x.dtype, device=x.device)
             moe_ops.grouped_gemm_tc(a, self.w_up, u, order, tile_expert, pairs, 0, first_act)
-            u = self._gate(u)
+            u, weights = self._gate(u, order, weights)
             y = torch.empty((pairs, self.hidden), dtype=x.dtype, device=x.device)
             moe_ops.grouped_gemm_tc(u, self.w_down, y, order, tile_expert, pairs, 1, weights=weights)
             return self._combine(x, y, gate)
@@ -158,18 +164,28 @@ class MoE(FeedForward):
         order, tile_expert = moe_ops.align(ids, self.E, tile)
         u = torch.empty((order.numel(), wide), dtype=x.dtype, device=x.device)
         moe_ops.grouped_gemm(x, self.w_up, u, order, tile_expert, pairs, self.top, tile, 0, first_act)
-        u = self._gate(u)
+        u, weights = self._gate(u, order, weights)
         y = torch.empty((pairs, self.hidden), dtype=x.dtype, device=x.device)
         moe_ops.grouped_gemm(u, self.w_down, y, order, tile_expert, pairs, self.top, tile, 1, weights=weights)
         return self._combine(x, y, gate)
 
-    def _gate(self, u):
-        """With a gate: the (gate, up) column pairs of the first product become act(gate) * up."""
+    def _gate(self, u, order, weights):
+        """With a gate: the (gate, up) column pairs of the first product become act(gate) * up.  Where the routing weight
+        belongs on the expert's input, both are multiplied by it first and the second product gets weights of one.
+        Returns (the second product's input, its weights)."""
         if not self.gated:
-            return u
+            return u, weights
         from ..kernels import ops
         out = torch.empty((u.shape[0], self.ff), dtype=u.dtype, device=u.device)
-        return ops.gated_act(u, out, self.activation, pairs=True)
+        if not self.weight_on_input:
+            return ops.gated_act(u, out, self.activation, pairs=True), weights
+        flat = weights.reshape(-1)
+        ones = self._ones.get(flat.numel())
+        if ones is None:
+            if len(self._ones) > 64:
+                self._ones.clear()
+            ones = self._ones[flat.numel()] = torch.ones_like(flat)
+        return ops.gated_act_scaled(u, out, flat, order, self.activation, pairs=True), ones
 
     def _combine(self, x, y, gate):
         shared = None

@@ -15,7 +15,8 @@ class RMSNorm(Norm):
     """params: ``size``, ``eps``, ``weight`` (tensor name after the prefix), ``optional`` (the weight may be absent
     from the file: the norm of a branch the layer does not have), ``scalar`` (the weight is one number for all
     coordinates, a tensor without dimensions: kept as ``gain``, and spread over the row for the kernels that take a
-    vector).
+    vector), ``offset`` (the file stores the weight around zero: the norm multiplies by ``offset + w``, kept in 32-bit
+    so that the stored digits survive the sum).
 
     ``out = T(v * rsqrt(mean(v^2) + eps) * w)`` with ``v = residual (+ delta)`` in 32-bit
     (crates/kernels/cuda/norm.cu:54-115, crates/layers/src/nn.rs:78-111)."""
@@ -27,14 +28,18 @@ class RMSNorm(Norm):
         self.weight_name = prefix + params.get("weight", "weight")
         self.optional = bool(params.get("optional", False))
         self.scalar = bool(params.get("scalar", False))
+        self.offset = float(params.get("offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
         self.gain: Optional[float] = None
 
     def declare(self) -> List[TensorDecl]:
-        return [TensorDecl(self.weight_name, () if self.scalar else (self.size,), init="ones", optional=self.optional)]
+        return [TensorDecl(self.weight_name, () if self.scalar else (self.size,), init="normal" if self.offset else "ones",
+                           optional=self.optional)]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         w = tensors.get(self.weight_name) if self.optional else tensors[self.weight_name]
+        if w is not None and self.offset:
+            w = w.to(torch.float32) + self.offset
         if w is not None and self.scalar:
             self.gain = float(w.float().item())
             w = w.reshape(1).expand(self.size)

@@ -58,6 +58,8 @@ class ModelSpec:
     embedding_scale: float = 1.0        # the embedding rows are multiplied by this on their way into the residual stream
     logit_softcap: float = 0.0          # > 0: logits = cap * tanh(logits / cap)
     logit_scale: float = 1.0            # the logits are multiplied by this (before a soft cap)
+    # what makes the first rows of the residual stream; None: a plain table (``embedding_tensor`` times ``embedding_scale``)
+    embedding: Optional[PartSpec] = None
 
     def check(self) -> None:
         if not self.layers:
