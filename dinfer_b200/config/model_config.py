@@ -872,6 +872,10 @@ class PorovikConfig:
                   architecture=str(d.get("architecture") or (d.get("architectures") or ["Porovik"])[0]))
         if cfg.vocab <= 0 or cfg.width <= 0 or cfg.max_positions <= 1:
             raise ConfigError("config.json: vocab and width must be positive, max_positions at least 2")
+        mixed = {(l.mixer.kv_heads, l.mixer.vdim) for l in cfg.layers if l.type == "attention" and l.mixer.v_mix}
+        if len(mixed) > 1:
+            raise ConfigError(f"config.json: layers with v_mix share the first one's values, so their kv_heads and vdim "
+                              f"must agree, got {sorted(mixed)}")
         if not cfg.norm_eps > 0:
             raise ConfigError(f"config.json: norm.eps must be positive, got {cfg.norm_eps}")
         return cfg

@@ -48,7 +48,8 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ldz, int* __restrict_
   if (gate && lane == 0) gate[t] = 1.f / (1.f + expf(-row[E]));      // the column behind the experts' is the gate's
   __syncwarp();
   if (sigmoid_scores) {
-    for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+    // the sigmoid keeps the order of the logits, so the choice is made on the logits themselves: scores that round
+    // to the same number (large logits all give 1) then still rank as the exact scores do
   } else {
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
@@ -74,6 +75,7 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ldz, int* __restrict_
       const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
       if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
     }
+    if (sigmoid_scores) best = 1.f / (1.f + expf(-best));
     if (lane == 0) {
       ids[(int64_t)t * top + k] = arg;
       weights[(int64_t)t * top + k] = best;

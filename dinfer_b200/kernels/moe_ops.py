@@ -78,7 +78,7 @@ def tc_grouped_supported(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tens
     """Whether a step's grouped products can run on the tcgen05 kernel: bfloat16, rows TMA can address, and enough rows."""
     E, ff, h = w_up.shape
     return (x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
-            and h % 8 == 0 and ff % 8 == 0 and pairs >= TC_MIN_ROWS_PER_EXPERT * E
+            and h % 8 == 0 and ff % 8 == 0 and w_down.shape[2] % 8 == 0 and pairs >= TC_MIN_ROWS_PER_EXPERT * E
             and w_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
 
 
