@@ -404,7 +404,34 @@ SOBIVIK_SIZES = {
     "medium": (_sobivik_cfg(2048, 16, 4, 128, 512, 1536, 1024, 7680), _qwen3_cfg(2048, 16, 4, 128, 7680)),
     "large": (_sobivik_cfg(4096, 32, 8, 128, 512, 1536, 1024, 12288), _qwen3_cfg(4096, 32, 8, 128, 12288)),
 }
-DESIGNS = {"dobedra": DESIGN_SIZES, "zasipel": ZASIPEL_SIZES, "sobivik": SOBIVIK_SIZES}
+
+
+# ---------------------------------------------------------------- Porovik beside Zasipel at equal layer sizes
+def _porovik_cfg(width, heads, kv_heads, dim, experts, top, ff_expert, ff_dense, vocab=32768):
+    gw = {"type": "hgrn2", "mixer": {"heads": heads, "dim": dim, "vdim": dim}}
+    gd = {"type": "general_delta", "mixer": {"heads": heads, "dim": dim, "decay_rank": dim // 2}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                          "q_temp": {"coef": 0.5, "every": 64}, "v_mix": True}}
+    dense = {"kind": "dense", "ff": ff_dense}
+    moe = {"kind": "moe", "expert": {"ff": ff_expert}, "router": {"experts": experts, "top": top}}
+    return {"architecture": "Porovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [dict(gw, mlp=dense), dict(att, mlp=moe), dict(gd, mlp=dense), dict(att, mlp=moe)]}
+
+
+# four layers (gate-write linear attention, attention with a distance bias, the general delta rule, attention again:
+# the second one mixes the first one's values into its own), heads of 64 or 128, a dense feed-forward behind the
+# recurrent mixers and 16 or 64 experts of which a token uses 2 or 6 behind the attention layers; beside each the
+# Zasipel layers of the same width, heads and experts (the closest design: a delta rule with a decay per channel,
+# attention, routed experts)
+POROVIK_SIZES = {
+    "small": (_porovik_cfg(1024, 16, 4, 64, 16, 2, 512, 2048), ZASIPEL_SIZES["small"][0]),
+    "medium": (_porovik_cfg(2048, 16, 4, 128, 64, 6, 1408, 7680), ZASIPEL_SIZES["medium"][0]),
+    "large": (_porovik_cfg(4096, 32, 8, 128, 64, 6, 2048, 12288), ZASIPEL_SIZES["large"][0]),
+}
+DESIGNS = {"dobedra": DESIGN_SIZES, "zasipel": ZASIPEL_SIZES, "sobivik": SOBIVIK_SIZES, "porovik": POROVIK_SIZES}
+# the model a design stands beside (the closest one this package has)
+BESIDE = {"porovik": "zasipel"}
 
 
 def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None):
@@ -466,15 +493,17 @@ def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None
 
 
 def design_run(a) -> int:
-    """``--design dobedra|zasipel|sobivik``: prefill and decode throughput of four layers of the design beside four Qwen3 layers
-    of the same width and head count, at the sizes of ``DESIGNS``; one JSON line."""
+    """``--design dobedra|zasipel|sobivik|porovik``: prefill and decode throughput of four layers of the design beside four
+    layers of the model it is compared with (Qwen3, or ``BESIDE``) at the same width and head count, at the sizes of
+    ``DESIGNS``; one JSON line."""
     rows = {}
     table = DESIGNS[a.design]
+    beside = BESIDE.get(a.design, "qwen3")
     sizes = [a.design_size] if a.design_size else list(table)
     for name in sizes:
         ours, theirs = table[name]
         row = {}
-        for label, cfg in ((a.design, ours), ("qwen3", theirs)):
+        for label, cfg in ((a.design, ours), (beside, theirs)):
             if a.profile and label != (a.design_model or a.design):
                 continue
             pre, dec, launches = _time_model(cfg, a.batch, a.context, PREFILL_TOKENS, a.steps, profile=a.profile)
@@ -484,7 +513,7 @@ def design_run(a) -> int:
         rows[name] = row
     if a.profile:
         return 0
-    print(json.dumps({"metric": f"{a.design.capitalize()} beside Qwen3, four layers at equal width and heads (bf16, random weights): "
+    print(json.dumps({"metric": f"{a.design.capitalize()} beside {beside.capitalize()}, four layers at equal width and heads (bf16, random weights): "
                                 f"prefill of {PREFILL_TOKENS} tokens, decode at batch {a.batch} context {a.context}",
                       "sizes": rows, "steps": a.steps, "impl": "ours", "data": "synthetic"}))
     return 0
@@ -509,11 +538,11 @@ def main() -> int:
     ap.add_argument("--closed-loop", default=None, metavar="C,P,O",
                     help="the reference's serving measurement at engine level instead: C clients, each sending its "
                          "next request when the last has ended, prompts of P tokens, O generated tokens (--shape applies)")
-    ap.add_argument("--design", choices=["dobedra", "zasipel", "sobivik"], default=None,
+    ap.add_argument("--design", choices=["dobedra", "zasipel", "sobivik", "porovik"], default=None,
                     help="instead of the benchmark: four layers of this design beside four Qwen3 layers of equal width, "
                          "prefill and decode, at a few layer sizes")
     ap.add_argument("--design-size", choices=["small", "medium", "large"], default=None, help="only this size")
-    ap.add_argument("--design-model", choices=["dobedra", "zasipel", "sobivik", "qwen3"], default=None, help="with --profile: which of the two")
+    ap.add_argument("--design-model", choices=["dobedra", "zasipel", "sobivik", "porovik", "qwen3"], default=None, help="with --profile: which of the two")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

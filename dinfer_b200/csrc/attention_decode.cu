@@ -40,6 +40,7 @@ struct Params {
   int H, Hkv, group, block_size, bs_log2, window;
   int sink;          // one more softmax term of score 0 without a value (the TMA variant)
   float scale_log2;
+  const float* slopes;   // [H] or null: a distance bias, score - slopes[h] * (i - j) (the TMA variant)
   int splits;
   float* part_o;     // [B, H, splits, D]
   float* part_ml;    // [B, H, splits, 2]
@@ -555,6 +556,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
       }
     }
     const int key_off = warp * 16;
+    float sl[NH8][2];                                          // the slopes of this thread's two heads, in log2 units
+#pragma unroll
+    for (int nt = 0; nt < NH8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int head = nt * 8 + tq * 2 + c;
+        sl[nt][c] = (p.slopes && head < p.group) ? p.slopes[hk * p.group + head] * 1.4426950408889634f : 0.f;
+      }
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int s = t % STAGES;
@@ -593,8 +602,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
         for (int nt = 0; nt < NH8; ++nt) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            const float s0 = vis0 ? st[nt][c] * p.scale_log2 : -INFINITY;
-            const float s1 = vis1 ? st[nt][c + 2] * p.scale_log2 : -INFINITY;
+            const float s0 = vis0 ? fmaf(st[nt][c], p.scale_log2, -sl[nt][c] * (float)(pos - jbase - g)) : -INFINITY;
+            const float s1 = vis1 ? fmaf(st[nt][c + 2], p.scale_log2, -sl[nt][c] * (float)(pos - jbase - g - 8)) : -INFINITY;
             float mx = fmaxf(s0, s1);
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
@@ -839,6 +848,7 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
   p.block_size = block_size; p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.sink = 0; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
+  p.slopes = nullptr;
   p.part_o = scratch_floats;
   p.part_ml = scratch_floats ? scratch_floats + (int64_t)B * H * splits * D : nullptr;
   p.counters = scratch_counters; p.status = nullptr;
@@ -851,11 +861,27 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
 // 16 of them), plus the number of pages of the cache tensor (for the tensor map) and the device status
 // word that a bounded wait sets when it runs out.
 // sink != 0: the softmax has one more term of score 0 that carries no value.
+// slopes: f32 [H] or null; with them score_ij - slopes[h] * (i - j).
+DINFER_API int dinfer_attention_decode_tma_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                                int64_t num_blocks, const int* block_table, int max_blocks,
+                                                const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
+                                                int block_size, float scale, int window, int sink, const float* slopes,
+                                                int splits, int* status, cudaStream_t stream);
+
 DINFER_API int dinfer_attention_decode_tma_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
                                                 int64_t num_blocks, const int* block_table, int max_blocks,
                                                 const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
                                                 int block_size, float scale, int window, int sink, int splits,
                                                 int* status, cudaStream_t stream) {
+  return dinfer_attention_decode_tma_bias(q, ldq, out, ldo, cache, num_blocks, block_table, max_blocks, cu_seqlens, seq_lens,
+                                          B, H, Hkv, D, block_size, scale, window, sink, nullptr, splits, status, stream);
+}
+
+DINFER_API int dinfer_attention_decode_tma_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                                int64_t num_blocks, const int* block_table, int max_blocks,
+                                                const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
+                                                int block_size, float scale, int window, int sink, const float* slopes,
+                                                int splits, int* status, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: bad sizes B=%d H=%d Hkv=%d", B, H, Hkv);
   if (!dinfer_attention_decode_supports(D, H / Hkv, block_size) || block_size < 8)
@@ -890,6 +916,7 @@ DINFER_API int dinfer_attention_decode_tma_sink(const void* q, int64_t ldq, void
   p.block_size = block_size; p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.sink = sink; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
+  p.slopes = slopes;
   p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.status = status;
   const int nh8 = (p.group + 7) / 8;
   if (D == 64) return nh8 == 1 ? launch_tma<64, 1>(map, p, B, stream) : launch_tma<64, 2>(map, p, B, stream);

@@ -46,6 +46,7 @@ struct Params {
   int B, H, Hkv, group, block_size, bs_log2, window;
   int sink;                    // one more softmax term of score 0 without a value
   float scale_log2;
+  const float* slopes;         // [H] or null: a distance bias, score - slopes[h] * (i - j)
   int* status;
 };
 
@@ -295,6 +296,8 @@ attention_umma64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int row = row0 + w * BM + r;
     const bool row_ok = row < rows_total;
     const int pos = row_ok ? hist + row / p.group : -1;
+    // the distance bias in the units of the raw scores (they are multiplied by scale_log2 later)
+    const float sl_raw = (p.slopes && row_ok) ? p.slopes[hk * p.group + row % p.group] * 1.4426950408889634f / p.scale_log2 : 0.f;
     const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
     const int first_tok_w = (row0 + w * BM) / p.group;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
@@ -310,6 +313,14 @@ attention_umma64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tmem_ld32(s_addr + (j & 1) * BN + 32, s1);
       tmem_ld_wait();
       const int jbase = (tile_begin + j) * BN;
+      if (p.slopes) {
+        const float d0 = (float)(jbase - pos);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          s0[i] = fmaf(sl_raw, d0 + (float)i, s0[i]);
+          s1[i] = fmaf(sl_raw, d0 + (float)(i + 32), s1[i]);
+        }
+      }
       const bool need_mask = (jbase + BN - 1 > hist + first_tok_w) || p.window > 0 || jbase < lo;
       if (need_mask) {
 #pragma unroll
@@ -455,11 +466,27 @@ DINFER_API int dinfer_attention_umma64_supports(int D, int group, int block_size
 // Prompt portions (q_len > 1) only; requests that bring one token are skipped.
 // q: [T, ...] rows of stride ldq with head h at h*D (all H heads); cache [num_blocks, 2, Hkv, block, D] bf16.
 // sink != 0: the softmax has one more term of score 0 that carries no value.
+// slopes: f32 [H] or null; with them score_ij - slopes[h] * (i - j).
+DINFER_API int dinfer_attention_umma64_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                     int64_t num_blocks, const int* block_table, int max_blocks,
+                                     const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
+                                     int block_size, float scale, int window, int sink, const float* slopes, int max_q_len,
+                                     int pair_bound, int* status, cudaStream_t stream);
+
 DINFER_API int dinfer_attention_umma64_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
                                      int64_t num_blocks, const int* block_table, int max_blocks,
                                      const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
                                      int block_size, float scale, int window, int sink, int max_q_len, int pair_bound,
                                      int* status, cudaStream_t stream) {
+  return dinfer_attention_umma64_bias(q, ldq, out, ldo, cache, num_blocks, block_table, max_blocks, cu_seqlens, seq_lens, T, B,
+                                      H, Hkv, D, block_size, scale, window, sink, nullptr, max_q_len, pair_bound, status, stream);
+}
+
+DINFER_API int dinfer_attention_umma64_bias(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                     int64_t num_blocks, const int* block_table, int max_blocks,
+                                     const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
+                                     int block_size, float scale, int window, int sink, const float* slopes, int max_q_len,
+                                     int pair_bound, int* status, cudaStream_t stream) {
   if (T <= 0 || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma64: bad sizes T=%d B=%d H=%d Hkv=%d", T, B, H, Hkv);
   const int group = H / Hkv;
@@ -504,6 +531,7 @@ DINFER_API int dinfer_attention_umma64_sink(const void* q, int64_t ldq, void* ou
   p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.sink = sink; p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.B = B;
+  p.slopes = slopes;
   // pairs of 128-row tiles in the batch: the caller's bound, or every request taken for the longest
   int64_t pairs = pair_bound > 0 ? pair_bound : (int64_t)B * (((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM));
   if (pairs > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_umma64: %lld row-tile pairs are too many for the grid", (long long)pairs);

@@ -60,11 +60,13 @@ def _decode_scratch(device, n_floats: int, n_counters: int):
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
-                     head_dim: int, scale: float, window: int, splits: int, sink: bool = False) -> torch.Tensor:
+                     head_dim: int, scale: float, window: int, splits: int, sink: bool = False,
+                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the requests that bring exactly one token (the others are skipped), keys split
     ``splits`` ways; the splits are folded inside the kernel.  ``sink``: one more softmax term of score 0 without a
-    value (pages of at least 8 tokens only)."""
-    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
+    value; ``slopes`` (f32 [H]): a distance bias ``score_ij - slopes[h] * (i - j)`` (both: pages of at least 8 tokens only)."""
+    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens, slopes)
+    _check_slopes(slopes, num_heads)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
     if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
@@ -80,16 +82,16 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
         # the splits of a (request, kv head) are one thread-block cluster and fold through shared memory
         from . import gemm_ops
         status = gemm_ops._state(q.device)["status"]
-        lib, f = _fn("attention_decode", "dinfer_attention_decode_tma_sink",
+        lib, f = _fn("attention_decode", "dinfer_attention_decode_tma_bias",
                      [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
-                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p])
         check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
                      block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), B, num_heads, num_kv_heads, head_dim,
-                     cache.shape[3], float(scale), int(window), int(bool(sink)), min(int(splits), MAX_CLUSTER_SPLITS),
+                     cache.shape[3], float(scale), int(window), int(bool(sink)), ptr(slopes), min(int(splits), MAX_CLUSTER_SPLITS),
                      ptr(status), stream_handle()), "attention_decode_tma")
         return out
-    if sink:
-        raise KernelError("attention_decode: the sink needs pages of at least 8 tokens")
+    if sink or slopes is not None:
+        raise KernelError("attention_decode: the sink and the distance bias need pages of at least 8 tokens")
     floats = counters = None
     if splits > 1:
         floats, counters = _decode_scratch(q.device, B * num_heads * splits * (head_dim + 2), B * num_kv_heads)
@@ -101,6 +103,11 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                  float(scale), int(window), int(splits), ptr(floats), ptr(counters), stream_handle()),
           "attention_decode")
     return out
+
+
+def _check_slopes(slopes, num_heads: int) -> None:
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != num_heads or not slopes.is_contiguous()):
+        raise KernelError("attention: slopes float32 [H]")
 
 
 def umma_supported(dtype: torch.dtype, head_dim: int, group: int, block_size: int) -> bool:
@@ -164,30 +171,32 @@ def umma_key_splits(portion_lens, group: int, num_kv_heads: int, head_dim: int, 
 def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                    cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
                    head_dim: int, scale: float, window: int, max_q_len: int, key_splits: int = 1,
-                   pair_bound: int = 0, sink: bool = False) -> torch.Tensor:
+                   pair_bound: int = 0, sink: bool = False, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the prompt portions of the batch (requests with more than one token; the others
     are skipped) on tcgen05 / TMEM / TMA.  ``q``: the [T, H*D] columns of the step's rows (a view with a
     row stride is fine).  ``key_splits``: see ``umma_key_splits``; ``pair_bound``: see ``umma_pair_bound``
-    (0: every request is taken for the longest portion)."""
+    (0: every request is taken for the longest portion); ``slopes`` (f32 [H]): a distance bias
+    ``score_ij - slopes[h] * (i - j)``."""
     _umma_launch(False, q, out, cache, block_table, cu_seqlens, seq_lens, num_heads, num_kv_heads, head_dim, scale,
-                 window, max_q_len, key_splits, pair_bound, sink)
+                 window, max_q_len, key_splits, pair_bound, sink, slopes)
     return out
 
 
 def attention_umma64(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
                      head_dim: int, scale: float, window: int, max_q_len: int, pair_bound: int = 0,
-                     sink: bool = False) -> torch.Tensor:
+                     sink: bool = False, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same attention through the kernel with 64-key tiles (``UMMA_SHORT_CONTEXT``); no key split."""
     _umma_launch(True, q, out, cache, block_table, cu_seqlens, seq_lens, num_heads, num_kv_heads, head_dim, scale,
-                 window, max_q_len, 1, pair_bound, sink)
+                 window, max_q_len, 1, pair_bound, sink, slopes)
     return out
 
 
 def _umma_launch(short, q, out, cache, block_table, cu_seqlens, seq_lens, num_heads, num_kv_heads, head_dim, scale,
-                 window, max_q_len, key_splits, pair_bound, sink=False) -> None:
+                 window, max_q_len, key_splits, pair_bound, sink=False, slopes=None) -> None:
     from . import gemm_ops
-    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
+    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens, slopes)
+    _check_slopes(slopes, num_heads)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_umma: bfloat16 only")
     if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
@@ -201,14 +210,14 @@ def _umma_launch(short, q, out, cache, block_table, cu_seqlens, seq_lens, num_he
     status = gemm_ops._state(q.device)["status"]
     head = (ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
             block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), q.shape[0], B, num_heads, num_kv_heads,
-            head_dim, cache.shape[3], float(scale), int(window), int(bool(sink)), int(max_q_len), int(pair_bound))
+            head_dim, cache.shape[3], float(scale), int(window), int(bool(sink)), ptr(slopes), int(max_q_len), int(pair_bound))
     types = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int]
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int]
     if short:
-        lib, f = _fn("attention_umma64", "dinfer_attention_umma64_sink", types + [c_void_p, c_void_p])
+        lib, f = _fn("attention_umma64", "dinfer_attention_umma64_bias", types + [c_void_p, c_void_p])
         check(lib, f(*head, ptr(status), stream_handle()), "attention_umma64")
     else:
-        lib, f = _fn("attention_umma", "dinfer_attention_umma_sink", types + [c_int, c_void_p, c_void_p])
+        lib, f = _fn("attention_umma", "dinfer_attention_umma_bias", types + [c_int, c_void_p, c_void_p])
         check(lib, f(*head, int(key_splits), ptr(status), stream_handle()), "attention_umma")
 
 

@@ -149,15 +149,12 @@ class GQAttention(Mixer):
         """Whether the tensor-core kernels take this attention: keys and values of one width."""
         return self.Dv == self.D and attention_ops.tc_supported(dtype, self.D, self.H // self.Hkv)
 
-    def _umma_ok(self) -> bool:
-        """The tcgen05 prompt kernels and the TMA decode kernel know no distance bias."""
-        return self.slopes is None and self.slope_values is None
 
     def kernel_libraries(self):
         att = ["attention_generic"]
         if self._fast(self.env.act_dtype):
             att = ["attention_tc"]
-            if self.D in (64, 128) and self._umma_ok():
+            if self.D in (64, 128):
                 att += ["attention_decode", "attention_umma", "attention_umma64"]
         return ["qk_post"] + att + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
@@ -219,14 +216,14 @@ class GQAttention(Mixer):
             splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, self.Hkv, ctx.max_seq_len)
             tc_decode = ctx.any_decode
             if ctx.any_decode and attention_ops.decode_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size) \
-                    and (g.block_size >= 8 or not self.sink) and self._umma_ok():
+                    and (g.block_size >= 8 or not (self.sink or self.slopes is not None)):
                 # decoded tokens: the kernel made for them (keys on the tile's rows, in-kernel fold)
                 attention_ops.attention_decode(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                               self.Hkv, self.D, self.scale, window, splits, sink=self.sink)
+                                               self.Hkv, self.D, self.scale, window, splits, sink=self.sink,
+                                               slopes=self.slopes)
                 tc_decode = False
             tc_prefill = ctx.any_prefill
-            if ctx.any_prefill and self._umma_ok() \
-                    and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
+            if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
                 # prompt portions: tcgen05 / TMEM / TMA
                 key = ("attention_umma", self.H, self.Hkv, self.D)
                 shape = ctx.derived.get(key)
@@ -241,11 +238,11 @@ class GQAttention(Mixer):
                         and attention_ops.umma64_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size)):
                     attention_ops.attention_umma64(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                                    self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[1],
-                                                   sink=self.sink)
+                                                   sink=self.sink, slopes=self.slopes)
                 else:
                     attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                                  self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[0], shape[1],
-                                                 sink=self.sink)
+                                                 sink=self.sink, slopes=self.slopes)
                 tc_prefill = False
             if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
