@@ -91,6 +91,11 @@ __device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async
 template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr int L_WARPS = 4;
+// tokens of a staged tile: 16, or 8 where 16 tokens' inputs would take so much shared memory that only two CTAs fit an SM
+// (the token loop is a chain: an SM is busy only with several CTAs' warps on it; measured at 32 heads of 128 x 128 with
+// the delta rule's five inputs: one 2048-token portion 964 us with 16 and 1010 with 8, four portions of 512 tokens 964
+// and 817)
+constexpr int tile_tokens(int dk, int inputs) { return dk * inputs >= 512 ? 8 : 16; }
 
 struct RowInput {          // rows of one per-token input: head h's channels at p[t * ld + h * dk ..]
   const float* p;
@@ -108,8 +113,8 @@ linear_state_kernel(RowInput r_in, RowInput k_in, RowInput w_in, RowInput u_in, 
                     const int* __restrict__ slots, const int* __restrict__ fresh, float* __restrict__ out, int H, int dk,
                     int dv, int vec) {
   constexpr int DK = R * LPC, COLS = 32 / LPC, BC = COLS * L_WARPS;
-  constexpr int TT = DK >= 256 ? 8 : 16;
   constexpr int NIN = REMOVE ? 5 : 2;
+  constexpr int TT = tile_tokens(DK, NIN);
   constexpr int TILE = TT * (NIN * DK + BC);               // floats of one staged tile: the inputs | v
   extern __shared__ __align__(16) float smf[];
   pdl_enter();
@@ -254,8 +259,8 @@ template <int R, int LPC, bool REMOVE>
 int launch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, const float* v, int64_t ldv, float* state,
                  int64_t state_stride, const int* cu, const int* slots, const int* fresh, float* out, int B, int H, int dk,
                  int dv, int vec, cudaStream_t stream) {
-  constexpr int DK = R * LPC, BC = 32 / LPC * L_WARPS, TT = DK >= 256 ? 8 : 16;
-  const size_t sm = (size_t)2 * TT * ((REMOVE ? 5 : 2) * DK + BC) * sizeof(float);
+  constexpr int DK = R * LPC, BC = 32 / LPC * L_WARPS, NIN = REMOVE ? 5 : 2, TT = tile_tokens(DK, NIN);
+  const size_t sm = (size_t)2 * TT * (NIN * DK + BC) * sizeof(float);
   static bool opted = false;
   if (sm > 48 * 1024 && !opted) {
     cudaError_t e = cudaFuncSetAttribute(linear_state_kernel<R, LPC, REMOVE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
@@ -275,11 +280,14 @@ int dispatch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, c
   auto ok = [](RowInput x) { return x.p == nullptr || (x.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x.p) & 15) == 0); };
   const int vec = dk % 4 == 0 && ok(r) && ok(k) && ok(w) && ok(u) && ok(p);
   // How many lanes share a column: a lane owns 16 rows, or 8 where there are too few (request, head, column) triples
-  // to put several warps on every scheduler (the token loop is a chain, so a warp issues only every few cycles).
+  // to put several warps on every scheduler (the token loop is a chain, so a warp issues only every few cycles); never
+  // more than 8 lanes a column, beyond which the longer exchange between the lanes costs more than the shorter step gains,
+  // unless the grid would not even give every SM a CTA (16 heads of 128 x 128, one portion: 726 us on 8 lanes, 671 on 16).
   static int sms = 0;
   if (!sms) { int d = 0; cudaGetDevice(&d); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d); if (sms <= 0) sms = 148; }
   const int base = DK == 256 ? 8 : DK / 16;
-  int wide = ((int64_t)B * H * dv * base / 32 < (int64_t)3 * 4 * sms) ? 1 : 0;
+  int wide = (base * 2 <= 8 && (int64_t)B * H * dv * base / 32 < (int64_t)3 * 4 * sms) ? 1 : 0;
+  if (DK == 128 && (int64_t)B * H * ((dv + 15) / 16) < sms) wide = 1;
   if (force_widen == 1) wide = 0;
   if (force_widen == 2) wide = 1;
 #define GO(R_, LPC_) return launch_state<R_, LPC_, REMOVE>(r, k, w, u, p, v, ldv, state, state_stride, cu, slots, fresh, out, B, H, dk, dv, vec, stream)
