@@ -411,11 +411,11 @@ def _porovik_cfg(width, heads, kv_heads, dim, experts, top, ff_expert, ff_dense,
     gw = {"type": "hgrn2", "mixer": {"heads": heads, "dim": dim, "vdim": dim}}
     gd = {"type": "general_delta", "mixer": {"heads": heads, "dim": dim, "decay_rank": dim // 2}}
     att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                                          "q_temp": {"coef": 0.5, "every": 64}, "v_mix": True}}
+                                          "q_temp": {"coef": 0.4, "every": 128}, "v_mix": True}}
     dense = {"kind": "dense", "ff": ff_dense}
     moe = {"kind": "moe", "expert": {"ff": ff_expert}, "router": {"experts": experts, "top": top}}
     return {"architecture": "Porovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 37}},
             "layers": [dict(gw, mlp=dense), dict(att, mlp=moe), dict(gd, mlp=dense), dict(att, mlp=moe)]}
 
 

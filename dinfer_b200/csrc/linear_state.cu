@@ -13,7 +13,7 @@
 //                        S are independent of one another, so a warp owns a few columns and the lanes of a column
 //                        share its rows.  Nothing but the order of a sum depends on how a request's tokens are cut
 //                        into steps, and the state between two steps is exact.  Key widths that are not 16, 32, 64,
-//                        128 or 256 run as the next of those with rows of zeros.
+//                        128, 256 or 512 run as the next of those with rows of zeros.
 //   tanh_rows            x <- tanh(x) on a block of columns (the middle of a thin two-matrix projection).
 //
 // A request whose `fresh` flag is set starts from a zero state (nothing is read from its slot).
@@ -95,7 +95,7 @@ constexpr int L_WARPS = 4;
 // (the token loop is a chain: an SM is busy only with several CTAs' warps on it; measured at 32 heads of 128 x 128 with
 // the delta rule's five inputs: one 2048-token portion 964 us with 16 and 1010 with 8, four portions of 512 tokens 964
 // and 817)
-constexpr int tile_tokens(int dk, int inputs) { return dk * inputs >= 512 ? 8 : 16; }
+constexpr int tile_tokens(int dk, int inputs) { return dk * inputs >= 2048 ? 4 : dk * inputs >= 512 ? 8 : 16; }
 
 struct RowInput {          // rows of one per-token input: head h's channels at p[t * ld + h * dk ..]
   const float* p;
@@ -281,7 +281,7 @@ template <bool REMOVE>
 int dispatch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, const float* v, int64_t ldv, float* state,
                    int64_t state_stride, const int* cu, const int* slots, const int* fresh, float* out, int B, int H,
                    int dk, int dv, int force_widen, cudaStream_t stream) {
-  const int DK = dk <= 16 ? 16 : dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : 256;
+  const int DK = dk <= 16 ? 16 : dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : dk <= 256 ? 256 : 512;
   auto ok = [](RowInput x) { return x.p == nullptr || (x.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x.p) & 15) == 0); };
   const int vec = dk % 4 == 0 && ok(r) && ok(k) && ok(w) && ok(u) && ok(p);
   // How many lanes share a column: a lane owns 16 rows, or 8 where there are too few (request, head, column) triples
@@ -290,7 +290,7 @@ int dispatch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, c
   // unless the grid would not even give every SM a CTA (16 heads of 128 x 128, one portion: 726 us on 8 lanes, 671 on 16).
   static int sms = 0;
   if (!sms) { int d = 0; cudaGetDevice(&d); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d); if (sms <= 0) sms = 148; }
-  const int base = DK == 256 ? 8 : DK / 16;
+  const int base = DK >= 256 ? 8 : DK / 16;
   int wide = (base * 2 <= 8 && (int64_t)B * H * dv * base / 32 < (int64_t)3 * 4 * sms) ? 1 : 0;
   if (DK == 128 && (int64_t)B * H * ((dv + 15) / 16) < sms) wide = 1;
   if (force_widen == 1) wide = 0;
@@ -306,7 +306,8 @@ int dispatch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, c
     case 128 * 2: GO(16, 8);
     case 128 * 2 + 1: GO(8, 16);
     case 256 * 2: GO(32, 8);
-    default: GO(16, 16);
+    case 256 * 2 + 1: GO(16, 16);
+    default: GO(32, 16);
   }
 #undef GO
 }
@@ -361,7 +362,7 @@ DINFER_API int dinfer_linear_state(const float* r, int64_t ldr, const float* k, 
                                    cudaStream_t stream) {
   if (B <= 0 || H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
     return refuse(DINFER_BAD_ARGUMENT, "linear_state: bad sizes B=%d H=%d dk=%d dv=%d", B, H, dk, dv);
-  if (dk > 256) return refuse(DINFER_BAD_ARGUMENT, "linear_state: %d key channels above the limit 256", dk);
+  if (dk > 512) return refuse(DINFER_BAD_ARGUMENT, "linear_state: %d key channels above the limit 512", dk);
   const int64_t nk = (int64_t)H * dk;
   if (!r || !w || !v || ldr < nk || ldw < nk || ldv < (int64_t)H * dv || (remove && (!k || !u || !p || ldk < nk || ldu < nk || ldp < nk)))
     return refuse(DINFER_BAD_ARGUMENT, "linear_state: an input is missing or its row stride is below its width");

@@ -77,12 +77,12 @@ POROVIK_D = model(257, 100, 2e-6, 260, None, [
     layer(general_delta(5, 20, 4), dense(36)),
     layer(hgrn2(2, 40, 36), None),
     layer(general_delta(1, 16, 1, vdim=48), moe(6, 2, 20))])
-# sizes of real layers in small: heads of 128 and 64, a delta rule of 128 key channels, eight experts
-POROVIK_E = model(400, 384, 5e-6, 640, (997, 31, 17), [
+# sizes of real layers in small: heads of 128 and 64, a delta rule of 128 key channels, eight and six experts
+POROVIK_E = model(400, 384, 5e-6, 640, (997, 29, 19), [
     layer(hgrn2(3, 64, 128), dense(448)),
-    layer(attention(4, 2, 128, 128, scale=0.09, temp=(0.5, 64), v_mix=True), moe(8, 2, 64)),
+    layer(attention(4, 2, 128, 128, scale=0.09, temp=(0.6, 48), v_mix=True), moe(8, 2, 64)),
     layer(general_delta(2, 128, 16), dense(256)),
-    layer(attention(8, 2, 64, 128, scale=0.12, v_mix=True), moe(8, 1, 64))])
+    layer(attention(8, 2, 64, 128, scale=0.12, v_mix=True), moe(6, 1, 48))])
 CONFIGS = {"A": POROVIK_A, "B": POROVIK_B, "C": POROVIK_C, "D": POROVIK_D, "E": POROVIK_E}
 
 

@@ -161,7 +161,7 @@ def test_general_delta(dtype, H_, dk, dv, width):
 
 @pytest.mark.parametrize("remove", [False, True])
 @pytest.mark.parametrize("widen", [1, 2])
-@pytest.mark.parametrize("H_, dk, dv", [(2, 16, 24), (1, 12, 20), (3, 64, 64), (5, 33, 7), (2, 128, 40), (1, 256, 8)])
+@pytest.mark.parametrize("H_, dk, dv", [(2, 16, 24), (1, 12, 20), (3, 64, 64), (5, 33, 7), (2, 128, 40), (1, 256, 8), (1, 300, 12)])
 def test_recurrence_forms(H_, dk, dv, widen, remove):
     """The kernel alone, both ways of sharing a column between lanes, against the recurrence in 64-bit: inputs that
     are views of wider rows at offsets no 16-byte load can take, requests of 1, 2, 16, 17 and 45 tokens in one batch,
@@ -246,7 +246,7 @@ def test_recurrence_remembers_a_far_token(remove):
 
 ATT = [  # heads, kv heads, dim, vdim, temperature, page size
     (4, 2, 8, 16, (0.7, 5), 16), (6, 1, 24, 40, (0.3, 1), 4), (3, 3, 10, 6, None, 16), (4, 1, 64, 64, (0.5, 16), 16),
-    (2, 2, 32, 32, None, 8), (4, 2, 128, 128, (0.5, 64), 16), (1, 1, 48, 32, (0.5, 7), 64)]
+    (2, 2, 32, 32, None, 8), (4, 2, 128, 128, (0.6, 48), 16), (1, 1, 40, 24, (0.4, 7), 64)]
 
 
 def att_params(H_, G, D, V, temp):
