@@ -442,7 +442,8 @@ DINFER_API int dinfer_delta_prep(const void* P, int64_t ldp, int cq, int ck, int
 DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* beta,
                                        const float* decay, float* state, int64_t state_stride, const int* cu,
                                        const int* slots, const int* fresh, float* out, int B, int H, int G, int dk,
-                                       int dv, int per_channel, int force_widen, cudaStream_t stream) {
+                                       int dv, int per_channel, int force_widen, int plain_launch,
+                                       cudaStream_t stream) {
   if (B <= 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
     return refuse(DINFER_BAD_ARGUMENT, "delta_recurrence: bad sizes B=%d H=%d G=%d dk=%d dv=%d", B, H, G, dk, dv);
   // key widths that split evenly over the lanes of a column (and rows that cp.async can fetch in 16-byte pieces): the
@@ -458,8 +459,15 @@ DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const f
       cudaFuncSetAttribute(delta_recurrence_reg_kernel<R_, LPC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
       opted = true;                                                                                                 \
     }                                                                                                               \
-    launch_pdl(delta_recurrence_reg_kernel<R_, LPC_>, dim3((dv + BC_ - 1) / BC_, H, B), dim3(R_WARPS * 32), sm, stream, qn, \
-               kn, vv, beta, decay, state, state_stride, cu, slots, fresh, out, H, G, dv, per_channel);             \
+    /* steps with portions of several tokens take a plain launch: launched programmatically behind the preparation   \
+       kernel, the CTAs land wherever an SM has room first, several to an SM, and the token loops run at the pace of  \
+       the fullest SM; a step of single tokens is short and gains from starting early */                              \
+    if (plain_launch)                                                                                               \
+      delta_recurrence_reg_kernel<R_, LPC_><<<dim3((dv + BC_ - 1) / BC_, H, B), dim3(R_WARPS * 32), sm, stream>>>(qn,    \
+          kn, vv, beta, decay, state, state_stride, cu, slots, fresh, out, H, G, dv, per_channel);                    \
+    else                                                                                                            \
+      launch_pdl(delta_recurrence_reg_kernel<R_, LPC_>, dim3((dv + BC_ - 1) / BC_, H, B), dim3(R_WARPS * 32), sm, stream, qn, \
+                 kn, vv, beta, decay, state, state_stride, cu, slots, fresh, out, H, G, dv, per_channel);           \
     return cuda_status("delta_recurrence");                                                                         \
   } while (0)
     // How many lanes share a column.  The token loop is a chain, so a warp issues an instruction every few cycles at

@@ -260,7 +260,7 @@ linear_state_kernel(RowInput r_in, RowInput k_in, RowInput w_in, RowInput u_in, 
 template <int R, int LPC, bool REMOVE>
 int launch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, const float* v, int64_t ldv, float* state,
                  int64_t state_stride, const int* cu, const int* slots, const int* fresh, float* out, int B, int H, int dk,
-                 int dv, int vec, cudaStream_t stream) {
+                 int dv, int vec, int plain_launch, cudaStream_t stream) {
   constexpr int DK = R * LPC, BC = 32 / LPC * L_WARPS, NIN = REMOVE ? 5 : 2, TT = tile_tokens(DK, NIN);
   const size_t sm = (size_t)2 * TT * (NIN * DK + BC) * sizeof(float);
   static bool opted = false;
@@ -269,18 +269,24 @@ int launch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, con
     if (e != cudaSuccess) return refuse((int)e, "linear_state: shared memory opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
-  // A plain launch, not a programmatic one: launched while the kernel before it still runs, the CTAs land wherever an SM
-  // has room first, several to an SM, and the token loops then run at the pace of the fullest SM (measured: a layer of
-  // 32 heads of 128 x 128 over 2048 tokens 2.86 ms so, 1.92 ms with the grid spread evenly).
-  linear_state_kernel<R, LPC, REMOVE><<<dim3((dv + BC - 1) / BC, H, B), dim3(L_WARPS * 32), sm, stream>>>(
-      r, k, w, u, p, v, ldv, state, state_stride, cu, slots, fresh, out, H, dk, dv, vec);
+  // Steps with portions of several tokens take a plain launch, not a programmatic one: launched while the kernel before
+  // it still runs, the CTAs land wherever an SM has room first, several to an SM, and the token loops then run at the
+  // pace of the fullest SM (measured: a layer of 32 heads of 128 x 128 over 2048 tokens 2.86 ms so, 1.92 ms with the
+  // grid spread evenly).  A step of single tokens is short and gains from starting early.
+  const dim3 grid((dv + BC - 1) / BC, H, B);
+  if (plain_launch)
+    linear_state_kernel<R, LPC, REMOVE><<<grid, dim3(L_WARPS * 32), sm, stream>>>(
+        r, k, w, u, p, v, ldv, state, state_stride, cu, slots, fresh, out, H, dk, dv, vec);
+  else
+    launch_pdl(linear_state_kernel<R, LPC, REMOVE>, grid, dim3(L_WARPS * 32), sm, stream, r, k, w, u, p, v, ldv, state,
+               state_stride, cu, slots, fresh, out, H, dk, dv, vec);
   return cuda_status("linear_state");
 }
 
 template <bool REMOVE>
 int dispatch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, const float* v, int64_t ldv, float* state,
                    int64_t state_stride, const int* cu, const int* slots, const int* fresh, float* out, int B, int H,
-                   int dk, int dv, int force_widen, cudaStream_t stream) {
+                   int dk, int dv, int force_widen, int plain_launch, cudaStream_t stream) {
   const int DK = dk <= 16 ? 16 : dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : dk <= 256 ? 256 : 512;
   auto ok = [](RowInput x) { return x.p == nullptr || (x.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x.p) & 15) == 0); };
   const int vec = dk % 4 == 0 && ok(r) && ok(k) && ok(w) && ok(u) && ok(p);
@@ -295,7 +301,7 @@ int dispatch_state(RowInput r, RowInput k, RowInput w, RowInput u, RowInput p, c
   if (DK == 128 && (int64_t)B * H * ((dv + 15) / 16) < sms) wide = 1;
   if (force_widen == 1) wide = 0;
   if (force_widen == 2) wide = 1;
-#define GO(R_, LPC_) return launch_state<R_, LPC_, REMOVE>(r, k, w, u, p, v, ldv, state, state_stride, cu, slots, fresh, out, B, H, dk, dv, vec, stream)
+#define GO(R_, LPC_) return launch_state<R_, LPC_, REMOVE>(r, k, w, u, p, v, ldv, state, state_stride, cu, slots, fresh, out, B, H, dk, dv, vec, plain_launch, stream)
   switch (DK * 2 + wide) {
     case 16 * 2: GO(16, 1);
     case 16 * 2 + 1: GO(8, 2);
@@ -355,11 +361,12 @@ DINFER_API int dinfer_tanh_rows(float* x, int64_t ld, int T, int n, cudaStream_t
 // gate-write form, inputs r and w only (k, u, p null).  v [T, ldv] (head h's columns at h * dv); state f32 rows
 // [slots, state_stride] whose first H * dk * dv floats hold S; out f32 [T, H * dv] contiguous.
 // force_widen: 0 the sizes decide, 1 a lane owns 16 rows, 2 a lane owns 8 (for tests; it only changes the order of sums).
+// plain_launch: for steps with portions of several tokens (see the launch).
 DINFER_API int dinfer_linear_state(const float* r, int64_t ldr, const float* k, int64_t ldk, const float* w, int64_t ldw,
                                    const float* u, int64_t ldu, const float* p, int64_t ldp, const float* v, int64_t ldv,
                                    float* state, int64_t state_stride, const int* cu, const int* slots, const int* fresh,
                                    float* out, int B, int H, int dk, int dv, int remove, int force_widen,
-                                   cudaStream_t stream) {
+                                   int plain_launch, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
     return refuse(DINFER_BAD_ARGUMENT, "linear_state: bad sizes B=%d H=%d dk=%d dv=%d", B, H, dk, dv);
   if (dk > 512) return refuse(DINFER_BAD_ARGUMENT, "linear_state: %d key channels above the limit 512", dk);
@@ -369,7 +376,7 @@ DINFER_API int dinfer_linear_state(const float* r, int64_t ldr, const float* k, 
   const RowInput R_{r, ldr}, W_{w, ldw};
   if (remove)
     return dispatch_state<true>(R_, RowInput{k, ldk}, W_, RowInput{u, ldu}, RowInput{p, ldp}, v, ldv, state, state_stride,
-                                cu, slots, fresh, out, B, H, dk, dv, force_widen, stream);
+                                cu, slots, fresh, out, B, H, dk, dv, force_widen, plain_launch, stream);
   return dispatch_state<false>(R_, RowInput{nullptr, 0}, W_, RowInput{nullptr, 0}, RowInput{nullptr, 0}, v, ldv, state,
-                               state_stride, cu, slots, fresh, out, B, H, dk, dv, force_widen, stream);
+                               state_stride, cu, slots, fresh, out, B, H, dk, dv, force_widen, plain_launch, stream);
 }

@@ -81,10 +81,12 @@ def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
         return out
     lib, f = _fn("delta_rule", "dinfer_delta_recurrence",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    B = cu_seqlens.numel() - 1
+    # a step with portions of several tokens (more rows than requests) spreads its CTAs evenly: see the kernel's launch
     check(lib, f(ptr(q), ptr(k), ptr(v), ptr(beta), ptr(decay), ptr(state), state.stride(0), ptr(cu_seqlens),
-                 ptr(slots), ptr(fresh), ptr(out), cu_seqlens.numel() - 1, H, G, dk, dv, int(bool(per_channel)),
-                 int(widen), stream_handle()), "delta_recurrence")
+                 ptr(slots), ptr(fresh), ptr(out), B, H, G, dk, dv, int(bool(per_channel)),
+                 int(widen), int(T > B), stream_handle()), "delta_recurrence")
     return out
 
 

@@ -103,8 +103,10 @@ def recurrence(r: torch.Tensor, w: torch.Tensor, v: torch.Tensor, state: torch.T
     lib, f = _fn("linear_state", "dinfer_linear_state",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                   c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                  c_int, c_void_p])
+                  c_int, c_int, c_void_p])
+    B = cu_seqlens.numel() - 1
+    # a step with portions of several tokens (more rows than requests) spreads its CTAs evenly: see the kernel's launch
     check(lib, f(ptr(r), st(r), ptr(k), st(k), ptr(w), st(w), ptr(u), st(u), ptr(p), st(p), ptr(v), st(v), ptr(state),
-                 state.stride(0), ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), cu_seqlens.numel() - 1, H, dk, dv,
-                 int(remove), int(widen), stream_handle()), "linear_state")
+                 state.stride(0), ptr(cu_seqlens), ptr(slots), ptr(fresh), ptr(out), B, H, dk, dv,
+                 int(remove), int(widen), int(T > B), stream_handle()), "linear_state")
     return out
